@@ -148,11 +148,21 @@ class CacheGroup:
         return [int(p) for p in self.table[slot, self.first_held[slot]:self.num_logical[slot]]]
 
 
+def _needs_of(need) -> list:
+    """A stage's needs as a list: a single need, none, a borrow, or a list of needs."""
+    if need is None:
+        return []
+    if isinstance(need, list):
+        return [n for n in need if n is not None]
+    return [need]
+
+
 class CacheManager:
     """Owns every group's pages and tables, the slots, and the per-slot state tensors.
 
-    stage_needs[s] is a `PagedNeed`, a `StateNeed`, None (the stage keeps nothing), or
-    ('borrow', t): stage s reads the cache of the earlier stage t.
+    stage_needs[s] is a `PagedNeed`, a `StateNeed`, None (the stage keeps nothing),
+    ('borrow', t): stage s reads the cache of the earlier stage t, or a list of needs: a stage whose
+    mixer is made of several keeps pages AND a state (at most one of each).
     """
 
     def __init__(self, stage_needs: Sequence, page_size: int, max_total_tokens: int, max_slots: int,
@@ -166,7 +176,8 @@ class CacheManager:
         self.max_slots = max_slots
         self.num_pages = (max_total_tokens + page_size - 1) // page_size
         # A request can be longer than the pool only if every group forgets old positions.
-        keeps_all = any(isinstance(n, PagedNeed) and n.window is None for n in stage_needs)
+        stage_needs = [_needs_of(n) for n in stage_needs]
+        keeps_all = any(isinstance(n, PagedNeed) and n.window is None for ns in stage_needs for n in ns)
         self.max_request_tokens = max_request_tokens or max_total_tokens
         if keeps_all:
             self.max_request_tokens = min(self.max_request_tokens, self.num_pages * page_size)
@@ -178,8 +189,10 @@ class CacheManager:
         self.stage_group: Dict[int, Tuple[int, int]] = {}     # stage -> (group index, index inside group)
         self.stage_state: Dict[int, StateNeed] = {}
         by_need: Dict[PagedNeed, int] = {}
-        for s, need in enumerate(stage_needs):
+        for s, need in ((s, n) for s, ns in enumerate(stage_needs) for n in ns):
             if isinstance(need, PagedNeed):
+                if s in self.stage_group:
+                    raise CacheError(f"stage {s} asks for pages twice")
                 gi = by_need.get(need)
                 if gi is None:
                     gi = len(self.groups)
@@ -189,8 +202,10 @@ class CacheManager:
                 self.stage_group[s] = (gi, len(g.stages))
                 g.stages.append(s)
             elif isinstance(need, StateNeed):
+                if s in self.stage_state:
+                    raise CacheError(f"stage {s} asks for a state twice")
                 self.stage_state[s] = need
-        for s, need in enumerate(stage_needs):
+        for s, need in ((s, n) for s, ns in enumerate(stage_needs) for n in ns):
             if isinstance(need, tuple) and need and need[0] == "borrow":
                 src = need[1]
                 if src not in self.stage_group:

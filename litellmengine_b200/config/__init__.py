@@ -5,10 +5,11 @@ from .registry import (ConfigError, config_class_for, config_from_dict, load_con
 from .specs import (BlockSpec, FeedForwardSpec, MixerSpec, ModelPlan, NormSpec,
                     PositionSpec, StageSpec)
 from .qwen3 import Qwen3Config
+from .tobovik import TobovikConfig
 
 __all__ = [
     "ConfigError", "config_class_for", "config_from_dict", "load_config",
     "register_architecture", "registered_architectures", "save_config",
     "unregister_architecture", "BlockSpec", "FeedForwardSpec", "MixerSpec", "ModelPlan",
-    "NormSpec", "PositionSpec", "StageSpec", "Qwen3Config",
+    "NormSpec", "PositionSpec", "StageSpec", "Qwen3Config", "TobovikConfig",
 ]

@@ -1,4 +1,4 @@
-"""One registry from an architecture's name (config.json `architectures[0]`) to
+"""One registry from an architecture's name (config.json `architectures[0]`, or `architecture`) to
 its configuration class.  The configuration class turns config.json into a
 `ModelPlan`; the model is then built from that plan by `parts.model.build_model`.
 
@@ -50,10 +50,14 @@ def config_class_for(name: str) -> type:
 
 
 def config_from_dict(d: dict):
+    """The architecture is named by `architectures` (a list, its first entry counts) or by `architecture`
+    (one string)."""
     archs = d.get("architectures")
-    if not isinstance(archs, list) or not archs or not isinstance(archs[0], str):
-        raise ConfigError("Missing required config field: architectures")
-    return config_class_for(archs[0]).from_dict(d)
+    if isinstance(archs, list) and archs and isinstance(archs[0], str):
+        return config_class_for(archs[0]).from_dict(d)
+    if isinstance(d.get("architecture"), str):
+        return config_class_for(d["architecture"]).from_dict(d)
+    raise ConfigError("Missing required config field: architectures")
 
 
 def load_config(model_dir: str):

@@ -18,9 +18,12 @@ from typing import Any, Dict, List, Optional, Tuple
 
 @dataclass(frozen=True)
 class NormSpec:
-    """A normalisation over the last dimension.  kind 'rmsnorm': x*rsqrt(mean(x^2)+eps)*w."""
+    """A normalisation over the last dimension.  kind 'rmsnorm': x*rsqrt(mean(x^2)+eps)*w.
+    `weight_name` is the local name of its weight tensor ('' when the tensor is named like the norm
+    itself, e.g. 'l0.norm1' instead of 'l0.norm1.weight')."""
     kind: str
     eps: float
+    weight_name: str = "weight"
 
 
 @dataclass(frozen=True)
@@ -28,7 +31,9 @@ class PositionSpec:
     """How a mixer encodes token positions.
 
     kind 'rope': half-split rotation of pairs (i, i+rotary_dim/2) by the angle
-    position * theta**(-2i/rotary_dim).  kind 'none': no encoding.
+    position * theta**(-2i/rotary_dim).  kind 'none': no encoding.  kind 'sinusoid_added' (a model's
+    `embedding_position`, not a mixer's): the vector with entry 2i = sin(p * theta**(-2i/width)) and
+    entry 2i+1 = cos of the same angle is added to the token's embedding.
     `params` carries what other kinds need.
     """
     kind: str
@@ -47,6 +52,19 @@ class MixerSpec:
     projects only queries and reads the keys and values another stage wrote (the
     stage that runs it must then name that stage in `cache_from`).  `params`
     carries what other kinds of mixer need.
+
+    kind 'gated_attention': the same attention with more of it configurable: values of their own width
+    (`value_dim`), biases on the q/k/v projections (`bias`), the q/k norm per head or over a token's whole
+    projection (`qk_norm_scope` 'head' | 'projection'), a query temperature (`query_temperature` = (coef,
+    every): q *= 1 + coef * ln(floor((p+1)/every) + 1)), an output gate on the concatenated heads
+    (`output_gate` 'sigmoid': times sigmoid(W_g x)).
+    kind 'gla': gated linear attention, a recurrent state [head_dim, value_dim] per head with a decay per
+    key channel; `params`: tau (alpha = sigmoid(z)^(1/tau)), rank (of the low-rank decay projection; None:
+    taken from the stored tensor).
+    kind 'parallel': the mixers in `branches` side by side on the same input, their results added with
+    the weights `branch_scales`.
+    `tensor_names` renames a mixer's tensors: pairs (the mixer's own name for a tensor, its name in the
+    model's files, without the mixer's prefix).
     """
     kind: str
     num_heads: int = 0
@@ -59,15 +77,25 @@ class MixerSpec:
     has_kv: bool = True
     weight_prefix: str = "self_attn"
     params: Tuple[Tuple[str, Any], ...] = ()
+    value_dim: Optional[int] = None        # None = head_dim
+    bias: bool = False
+    qk_norm_scope: str = "head"
+    query_temperature: Optional[Tuple[float, int]] = None
+    output_gate: Optional[str] = None
+    branches: Tuple["MixerSpec", ...] = ()
+    branch_scales: Tuple[float, ...] = ()
+    tensor_names: Tuple[Tuple[str, str], ...] = ()
 
 
 @dataclass(frozen=True)
 class FeedForwardSpec:
-    """The per-token part of a layer.  kind 'swiglu': down(silu(gate(x)) * up(x))."""
+    """The per-token part of a layer.  kind 'swiglu': down(silu(gate(x)) * up(x)).
+    `tensor_names`: pairs (the part's own name for a tensor, its name in the model's files)."""
     kind: str
     intermediate_size: int = 0
     weight_prefix: str = "mlp"
     params: Tuple[Tuple[str, Any], ...] = ()
+    tensor_names: Tuple[Tuple[str, str], ...] = ()
 
 
 @dataclass(frozen=True)
@@ -75,10 +103,13 @@ class BlockSpec:
     """One layer: which parts it has and how they are wired.
 
     arrangement 'pre_norm': h += mixer(norm1(h)); h += ffn(norm2(h)).
+    arrangement 'branch_norm': h += norm1(mixer(h)); h += norm2(ffn(h)): the norms sit on the sublayers'
+    outputs, and the sublayers read the stream itself.
+    `feed_forward` None: a layer that is its mixer only.
     """
     arrangement: str
     mixer: MixerSpec
-    feed_forward: FeedForwardSpec
+    feed_forward: Optional[FeedForwardSpec]
     mixer_norm: NormSpec
     feed_forward_norm: NormSpec
     weight_prefix: str = ""
@@ -111,6 +142,7 @@ class ModelPlan:
     embedding_name: str = "model.embed_tokens.weight"
     final_norm_name: str = "model.norm.weight"
     output_name: str = "lm_head.weight"
+    embedding_position: Optional[PositionSpec] = None     # an encoding added to the embeddings themselves
 
     def validate(self) -> None:
         if self.hidden_size <= 0 or self.vocab_size <= 0:

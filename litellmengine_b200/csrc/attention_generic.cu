@@ -19,6 +19,13 @@
 // which tile depends only on (lo, p), never on the batch, so a position's result does not depend
 // on how the work was cut.  (With one warp per (token, head) a decode step of 8 requests at a
 // context of 4,096 kept two warps an SM busy: 5 ms a layer.)
+//
+// Keys and values may differ in width (dk, dv) and live in tensors of their own: `keys` [pages, nkv,
+// page, dk] and `values` [pages, nkv, page, dv], each with its own page stride (the two halves of one
+// [pages, 2, nkv, page, d] tensor are the special case dk == dv).  An optional output gate is applied
+// before the store: out = o * sigmoid(gate[t, gate_off + h*dv + i]) * out_scale, and the output row
+// may be a column range of a wider buffer (`out_stride`, `out_off`), which is how a layer that runs
+// several mixers side by side collects their results for ONE output product.
 #include "common.cuh"
 #include <math_constants.h>
 
@@ -27,11 +34,13 @@
 
 template <typename T, typename TC>
 __global__ void paged_attention_generic_kernel(
-    const T* __restrict__ q, T* __restrict__ out, const TC* __restrict__ cache,
+    const T* __restrict__ q, T* __restrict__ out, const TC* __restrict__ keys, const TC* __restrict__ values,
+    long long key_page_stride, long long value_page_stride,
     const int32_t* __restrict__ positions, const int32_t* __restrict__ token_entry,
     const int32_t* __restrict__ entry_slot, const int32_t* __restrict__ block_table, int table_stride,
-    int num_tokens, int nq, int nkv, int d, int page_size, int window, float scale, int num_pages,
-    int32_t* __restrict__ status) {
+    int num_tokens, int nq, int nkv, int d, int dv, int page_size, int window, float scale, int num_pages,
+    const float* __restrict__ gate, long long gate_stride, int gate_off, float out_scale,
+    long long out_stride, int out_off, int vec, int32_t* __restrict__ status) {
     pdl_begin();
     extern __shared__ float smem[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -40,7 +49,7 @@ __global__ void paged_attention_generic_kernel(
     const int h = static_cast<int>(item - static_cast<long long>(t) * nq);
     const int kvh = h / (nq / nkv);
     float* qs = smem;                                  // [d]
-    float* merge = smem + d;                           // [AG_WARPS][d + 2]: output, maximum, sum of each warp
+    float* merge = smem + d;                           // [AG_WARPS][dv + 2]: output, maximum, sum of each warp
     const T* qrow = q + (static_cast<size_t>(t) * nq + h) * d;
     for (int i = threadIdx.x; i < d; i += AG_WARPS * 32) qs[i] = to_f32(qrow[i]) * scale;
     __syncthreads();
@@ -49,8 +58,8 @@ __global__ void paged_attention_generic_kernel(
     const int slot = entry_slot[token_entry[t]];
     const int32_t* table = block_table + static_cast<size_t>(slot) * table_stride;
     const int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
-    const size_t head_stride = static_cast<size_t>(page_size) * d;       // one kv head inside a page
-    const size_t page_stride = 2 * static_cast<size_t>(nkv) * head_stride;
+    const size_t khead = static_cast<size_t>(page_size) * d;        // one kv head inside a page of keys
+    const size_t vhead = static_cast<size_t>(page_size) * dv;       // and inside a page of values
 
     float m = -CUDART_INF_F, l = 0.0f;
     float acc[AG_MAX_D / 32];
@@ -60,7 +69,7 @@ __global__ void paged_attention_generic_kernel(
     for (int base = lo + 32 * warp; base <= pos; base += 32 * AG_WARPS) {
         const int j = base + lane;
         const bool valid = j <= pos;
-        long long koff = -1;
+        long long voff = -1;
         float s = -CUDART_INF_F;
         if (valid) {
             const int logical = j / page_size;
@@ -68,87 +77,100 @@ __global__ void paged_attention_generic_kernel(
             if (page < 0 || page >= num_pages) {
                 if (atomicCAS(status, 0, 4) == 0) status[1] = t;
             } else {
-                koff = static_cast<long long>(page) * page_stride + kvh * head_stride +
-                       static_cast<size_t>(j % page_size) * d;
-                const TC* kr = cache + koff;
+                const TC* kr = keys + static_cast<long long>(page) * key_page_stride + kvh * khead +
+                               static_cast<size_t>(j % page_size) * d;
+                voff = static_cast<long long>(page) * value_page_stride + kvh * vhead +
+                       static_cast<size_t>(j % page_size) * dv;
                 float dot = 0.0f;
-                for (int i = 0; i < d; i += 8) {
-                    float kv[8];
-                    load8(kr + i, kv);
+                if (vec) {
+                    for (int i = 0; i < d; i += 8) {
+                        float kv[8];
+                        load8(kr + i, kv);
 #pragma unroll
-                    for (int u = 0; u < 8; ++u) dot += qs[i + u] * kv[u];
+                        for (int u = 0; u < 8; ++u) dot += qs[i + u] * kv[u];
+                    }
+                } else {
+                    for (int i = 0; i < d; ++i) dot += qs[i] * to_f32(kr[i]);
                 }
                 s = dot;
             }
         }
         const float m_new = fmaxf(m, warp_max(s));
-        const float p = (koff >= 0) ? expf(s - m_new) : 0.0f;
+        const float p = (voff >= 0) ? expf(s - m_new) : 0.0f;
         const float alpha = (m == -CUDART_INF_F) ? 0.0f : expf(m - m_new);
         l = l * alpha + warp_sum(p);
         m = m_new;
 #pragma unroll
         for (int r = 0; r < AG_MAX_D / 32; ++r) acc[r] *= alpha;
         const int count = min(32, pos - base + 1);
-        const long long voff = koff + static_cast<long long>(nkv) * head_stride;   // V follows K in a page
         for (int jj = 0; jj < count; ++jj) {
             const float pj = __shfl_sync(0xffffffffu, p, jj);
             const long long vo = __shfl_sync(0xffffffffu, voff, jj);
             if (pj == 0.0f) continue;                  // also skips keys whose page was refused
-            const TC* vr = cache + vo;
+            const TC* vr = values + vo;
 #pragma unroll
             for (int r = 0; r < AG_MAX_D / 32; ++r) {
                 const int i = lane + 32 * r;
-                if (i < d) acc[r] += pj * to_f32(vr[i]);
+                if (i < dv) acc[r] += pj * to_f32(vr[i]);
             }
         }
     }
     // merge the warps' partial results, in warp order (a warp without tiles has m = -inf, l = 0)
-    float* mine = merge + warp * (d + 2);
+    float* mine = merge + warp * (dv + 2);
 #pragma unroll
     for (int r = 0; r < AG_MAX_D / 32; ++r) {
         const int i = lane + 32 * r;
-        if (i < d) mine[i] = acc[r];
+        if (i < dv) mine[i] = acc[r];
     }
-    if (lane == 0) { mine[d] = m; mine[d + 1] = l; }
+    if (lane == 0) { mine[dv] = m; mine[dv + 1] = l; }
     __syncthreads();
     float m_all = -CUDART_INF_F;
-    for (int w2 = 0; w2 < AG_WARPS; ++w2) m_all = fmaxf(m_all, merge[w2 * (d + 2) + d]);
+    for (int w2 = 0; w2 < AG_WARPS; ++w2) m_all = fmaxf(m_all, merge[w2 * (dv + 2) + dv]);
     float l_all = 0.0f;
     for (int w2 = 0; w2 < AG_WARPS; ++w2) {
-        const float mw = merge[w2 * (d + 2) + d];
-        if (mw != -CUDART_INF_F) l_all += merge[w2 * (d + 2) + d + 1] * expf(mw - m_all);
+        const float mw = merge[w2 * (dv + 2) + dv];
+        if (mw != -CUDART_INF_F) l_all += merge[w2 * (dv + 2) + dv + 1] * expf(mw - m_all);
     }
-    T* orow = out + (static_cast<size_t>(t) * nq + h) * d;
+    T* orow = out + static_cast<size_t>(t) * out_stride + out_off + static_cast<size_t>(h) * dv;
+    const float* grow = gate ? gate + static_cast<size_t>(t) * gate_stride + gate_off + static_cast<size_t>(h) * dv : nullptr;
     const float inv = 1.0f / l_all;
-    for (int i = threadIdx.x; i < d; i += AG_WARPS * 32) {
+    for (int i = threadIdx.x; i < dv; i += AG_WARPS * 32) {
         float o = 0.0f;
         for (int w2 = 0; w2 < AG_WARPS; ++w2) {
-            const float mw = merge[w2 * (d + 2) + d];
-            if (mw != -CUDART_INF_F) o += merge[w2 * (d + 2) + i] * expf(mw - m_all);
+            const float mw = merge[w2 * (dv + 2) + dv];
+            if (mw != -CUDART_INF_F) o += merge[w2 * (dv + 2) + i] * expf(mw - m_all);
         }
-        orow[i] = from_f32<T>(o * inv);
+        o *= inv;
+        if (grow) o *= 1.0f / (1.0f + expf(-grow[i]));
+        orow[i] = from_f32<T>(o * out_scale);
     }
 }
 
-extern "C" int llm_paged_attention_generic(
-    const void* q, void* out, int dtype, const void* cache, int cache_dtype, const int32_t* positions,
+// The general entry point: keys and values by their own pointers, widths and page strides (in
+// elements), optional output gate and scale, output as a column range of a wider buffer.
+extern "C" int llm_paged_attention_generic_kv(
+    const void* q, void* out, int dtype, const void* keys, const void* values, int cache_dtype,
+    long long key_page_stride, long long value_page_stride, const int32_t* positions,
     const int32_t* token_entry, const int32_t* entry_slot, const int32_t* block_table, int table_stride,
-    int num_tokens, int nq, int nkv, int d, int page_size, int window, float scale, int num_pages,
+    int num_tokens, int nq, int nkv, int d, int dv, int page_size, int window, float scale, int num_pages,
+    const float* gate, long long gate_stride, int gate_off, float out_scale, long long out_stride, int out_off,
     int32_t* status, uintptr_t stream) {
     if (num_tokens <= 0) return LLM_OK;
-    if (nq <= 0 || nkv <= 0 || nq % nkv != 0 || d <= 0 || d > AG_MAX_D || (d & 15) || page_size <= 0)
+    if (nq <= 0 || nkv <= 0 || nq % nkv != 0 || d <= 0 || d > AG_MAX_D || dv <= 0 || dv > AG_MAX_D || page_size <= 0)
         return LLM_REFUSED_SIZE;
-    if (!aligned16(cache)) return LLM_REFUSED_ALIGN;
-    const size_t smem = (static_cast<size_t>(d) + static_cast<size_t>(AG_WARPS) * (d + 2)) * sizeof(float);
+    const int esz = cache_dtype == LLM_DT_F32 ? 4 : 2;
+    const int vec = (d % 8 == 0) && aligned16(keys) && (key_page_stride * esz) % 16 == 0;
+    const size_t smem = (static_cast<size_t>(d) + static_cast<size_t>(AG_WARPS) * (dv + 2)) * sizeof(float);
     const long long items = static_cast<long long>(num_tokens) * nq;
     if (items > 0x7fffffffLL) return LLM_REFUSED_SIZE;
     const unsigned blocks = static_cast<unsigned>(items);
     cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
 #define LAUNCH(T, TC)                                                                              \
     launch_pdl((paged_attention_generic_kernel<T, TC>), dim3(blocks), dim3(AG_WARPS * 32), smem, s,                      \
-        static_cast<const T*>(q), static_cast<T*>(out), static_cast<const TC*>(cache), positions,  \
-        token_entry, entry_slot, block_table, table_stride, num_tokens, nq, nkv, d, page_size,     \
-        window, scale, num_pages, status)
+        static_cast<const T*>(q), static_cast<T*>(out), static_cast<const TC*>(keys),               \
+        static_cast<const TC*>(values), key_page_stride, value_page_stride, positions,             \
+        token_entry, entry_slot, block_table, table_stride, num_tokens, nq, nkv, d, dv, page_size, \
+        window, scale, num_pages, gate, gate_stride, gate_off, out_scale, out_stride, out_off, vec, status)
     if (dtype == LLM_DT_F32 && cache_dtype == LLM_DT_F32) LAUNCH(float, float);
     else if (dtype == LLM_DT_BF16 && cache_dtype == LLM_DT_BF16) LAUNCH(bf16, bf16);
     else if (dtype == LLM_DT_F32 && cache_dtype == LLM_DT_BF16) LAUNCH(float, bf16);
@@ -156,4 +178,23 @@ extern "C" int llm_paged_attention_generic(
     else return LLM_REFUSED_DTYPE;
 #undef LAUNCH
     return launch_status();
+}
+
+// Keys and values of equal width in one tensor [pages, 2, nkv, page, d]: the values follow the keys
+// inside a page.
+extern "C" int llm_paged_attention_generic(
+    const void* q, void* out, int dtype, const void* cache, int cache_dtype, const int32_t* positions,
+    const int32_t* token_entry, const int32_t* entry_slot, const int32_t* block_table, int table_stride,
+    int num_tokens, int nq, int nkv, int d, int page_size, int window, float scale, int num_pages,
+    int32_t* status, uintptr_t stream) {
+    if (num_tokens <= 0) return LLM_OK;
+    if (nq <= 0 || nkv <= 0 || d <= 0 || (d & 15) || page_size <= 0) return LLM_REFUSED_SIZE;
+    if (!aligned16(cache)) return LLM_REFUSED_ALIGN;
+    const long long half = static_cast<long long>(nkv) * page_size * d;
+    const char* base = static_cast<const char*>(cache);
+    return llm_paged_attention_generic_kv(q, out, dtype, base, base + half * (cache_dtype == LLM_DT_F32 ? 4 : 2),
+                                          cache_dtype, 2 * half, 2 * half, positions, token_entry, entry_slot,
+                                          block_table, table_stride, num_tokens, nq, nkv, d, d, page_size, window,
+                                          scale, num_pages, nullptr, 0, 0, 1.0f, static_cast<long long>(nq) * d, 0,
+                                          status, stream);
 }

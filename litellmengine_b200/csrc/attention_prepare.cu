@@ -1,0 +1,181 @@
+// Everything between the q/k/v projection and the attention kernel, for attention layers that are
+// not of the "per-head norm, then rotation" kind that `rope_cache.cu` fuses.  One block per token:
+//
+//   q = proj[t, q_off : q_off + nq*dk] (+ bq)        k = proj[t, k_off : ...] (+ bk)      v likewise (+ bv)
+//   norm (32-bit), by `norm_scope`:
+//       0  none
+//       1  per head:        x_head * rsqrt(mean(x_head^2) + eps) * w[i mod dk]
+//       2  whole projection: x * rsqrt(mean over ALL heads' entries of x^2 + eps) * w[i]
+//   query temperature (optional): q *= 1 + coef * ln(floor((p + 1) / every) + 1), p the token's position
+//   q is stored in the compute dtype [T, nq*dk]; k and v go to the token's place in its request's
+//   pages, `keys` [pages, nkv, page, dk] and `values` [pages, nkv, page, dv] (any page strides, so that
+//   the two halves of one [pages, 2, nkv, page, d] tensor are served as well as tensors of their own).
+//
+// `proj` is float32 (the projection's accumulators, never rounded on their way here), `proj_stride`
+// floats from token to token: the three pieces may be columns of a wider product.
+#include "common.cuh"
+
+#define AP_THREADS 256
+
+template <typename TQ, typename TC>
+__global__ void attention_prepare_kernel(
+    const float* __restrict__ proj, long long proj_stride, int q_off, int k_off, int v_off,
+    const float* __restrict__ bq, const float* __restrict__ bk, const float* __restrict__ bv,
+    const float* __restrict__ qw, const float* __restrict__ kw, int norm_scope, float eps,
+    float temp_coef, int temp_every,
+    TQ* __restrict__ q_out, TC* __restrict__ keys, TC* __restrict__ values,
+    long long key_page_stride, long long value_page_stride,
+    const int32_t* __restrict__ positions, const int32_t* __restrict__ token_entry,
+    const int32_t* __restrict__ entry_slot, const int32_t* __restrict__ block_table, int table_stride,
+    int nq, int nkv, int dk, int dv, int page_size, int num_pages, int32_t* __restrict__ status) {
+    pdl_begin();
+    extern __shared__ __align__(16) float smem[];
+    const int nqe = nq * dk, nke = nkv * dk, nve = nkv * dv;
+    float* fq = smem;                       // [nq*dk]
+    float* fk = smem + nqe;                 // [nkv*dk]
+    float* scratch = fk + nke;              // 33
+    const int t = blockIdx.x;
+    const float* row = proj + static_cast<size_t>(t) * proj_stride;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
+
+    float ssq = 0.0f, ssk = 0.0f;
+    for (int i = threadIdx.x; i < nqe; i += blockDim.x) {
+        const float a = row[q_off + i] + (bq ? bq[i] : 0.0f);
+        fq[i] = a;
+        ssq += a * a;
+    }
+    if (keys)
+        for (int i = threadIdx.x; i < nke; i += blockDim.x) {
+            const float a = row[k_off + i] + (bk ? bk[i] : 0.0f);
+            fk[i] = a;
+            ssk += a * a;
+        }
+    if (norm_scope == 2) {
+        const float tq = block_sum(ssq, scratch);
+        const float iq = 1.0f / sqrtf(tq / static_cast<float>(nqe) + eps);
+        for (int i = threadIdx.x; i < nqe; i += blockDim.x) fq[i] = fq[i] * iq * (qw ? qw[i] : 1.0f);
+        if (keys) {
+            const float tk = block_sum(ssk, scratch);
+            const float ik = 1.0f / sqrtf(tk / static_cast<float>(nke) + eps);
+            for (int i = threadIdx.x; i < nke; i += blockDim.x) fk[i] = fk[i] * ik * (kw ? kw[i] : 1.0f);
+        }
+    } else if (norm_scope == 1) {
+        __syncthreads();
+        for (int head = warp; head < nq + (keys ? nkv : 0); head += nwarps) {      // a warp per head
+            float* x = head < nq ? fq + head * dk : fk + (head - nq) * dk;
+            const float* w = head < nq ? qw : kw;
+            float ss = 0.0f;
+            for (int i = lane; i < dk; i += 32) ss += x[i] * x[i];
+            ss = warp_sum(ss);
+            const float inv = 1.0f / sqrtf(ss / static_cast<float>(dk) + eps);
+            for (int i = lane; i < dk; i += 32) x[i] = x[i] * inv * (w ? w[i] : 1.0f);
+        }
+    }
+    __syncthreads();
+
+    const int pos = positions[t];
+    float temp = 1.0f;
+    if (temp_every > 0) temp = 1.0f + temp_coef * logf(static_cast<float>((pos + 1) / temp_every + 1));
+    TQ* qo = q_out + static_cast<size_t>(t) * nqe;
+    for (int i = threadIdx.x; i < nqe; i += blockDim.x) qo[i] = from_f32<TQ>(fq[i] * temp);
+    if (!keys) return;
+
+    const int slot = entry_slot[token_entry[t]];
+    const int logical = pos / page_size;
+    const int page = logical < table_stride ? block_table[static_cast<size_t>(slot) * table_stride + logical] : -1;
+    if (page < 0 || page >= num_pages) {
+        if (threadIdx.x == 0 && atomicCAS(status, 0, 3) == 0) status[1] = t;
+        return;
+    }
+    const int in_page = pos % page_size;
+    TC* kp = keys + static_cast<size_t>(page) * key_page_stride;
+    TC* vp = values + static_cast<size_t>(page) * value_page_stride;
+    for (int i = threadIdx.x; i < nke; i += blockDim.x) {
+        const int head = i / dk, e = i - head * dk;
+        kp[(static_cast<size_t>(head) * page_size + in_page) * dk + e] = from_f32<TC>(fk[i]);
+    }
+    for (int i = threadIdx.x; i < nve; i += blockDim.x) {
+        const int head = i / dv, e = i - head * dv;
+        vp[(static_cast<size_t>(head) * page_size + in_page) * dv + e] =
+            from_f32<TC>(row[v_off + i] + (bv ? bv[i] : 0.0f));
+    }
+}
+
+extern "C" int llm_attention_prepare(
+    const float* proj, long long proj_stride, int q_off, int k_off, int v_off, const float* bq, const float* bk,
+    const float* bv, const float* qw, const float* kw, int norm_scope, float eps, float temp_coef, int temp_every,
+    void* q_out, int q_dtype, void* keys, void* values, int cache_dtype, long long key_page_stride,
+    long long value_page_stride, const int32_t* positions, const int32_t* token_entry, const int32_t* entry_slot,
+    const int32_t* block_table, int table_stride, int num_tokens, int nq, int nkv, int dk, int dv, int page_size,
+    int num_pages, int32_t* status, uintptr_t stream) {
+    if (num_tokens <= 0) return LLM_OK;
+    if (nq <= 0 || nkv < 0 || dk <= 0 || dv <= 0 || norm_scope < 0 || norm_scope > 2 || temp_every < 0)
+        return LLM_REFUSED_SIZE;
+    if (keys && (!values || !block_table || page_size <= 0)) return LLM_REFUSED_SIZE;
+    const size_t smem = (static_cast<size_t>(nq) * dk + static_cast<size_t>(nkv) * dk + 33) * sizeof(float);
+    if (smem > 200 * 1024) return LLM_REFUSED_SIZE;
+    cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+    if (!keys) cache_dtype = q_dtype;
+#define LAUNCH(TQ, TC)                                                                                            \
+    do {                                                                                                          \
+        auto kern = attention_prepare_kernel<TQ, TC>;                                                             \
+        if (smem > 48 * 1024) {                                                                                   \
+            const cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,         \
+                                                       static_cast<int>(smem));                                   \
+            if (e != cudaSuccess) return static_cast<int>(e);                                                     \
+        }                                                                                                         \
+        launch_pdl(kern, dim3(num_tokens), dim3(AP_THREADS), smem, s, proj, proj_stride, q_off, k_off, v_off, bq, \
+                   bk, bv, qw, kw, norm_scope, eps, temp_coef, temp_every, static_cast<TQ*>(q_out),               \
+                   static_cast<TC*>(keys), static_cast<TC*>(values), key_page_stride, value_page_stride,          \
+                   positions, token_entry, entry_slot, block_table, table_stride, nq, nkv, dk, dv, page_size,     \
+                   num_pages, status);                                                                            \
+    } while (0)
+    if (q_dtype == LLM_DT_F32 && cache_dtype == LLM_DT_F32) LAUNCH(float, float);
+    else if (q_dtype == LLM_DT_BF16 && cache_dtype == LLM_DT_BF16) LAUNCH(bf16, bf16);
+    else if (q_dtype == LLM_DT_F32 && cache_dtype == LLM_DT_BF16) LAUNCH(float, bf16);
+    else if (q_dtype == LLM_DT_BF16 && cache_dtype == LLM_DT_F32) LAUNCH(bf16, float);
+    else return LLM_REFUSED_DTYPE;
+#undef LAUNCH
+    return launch_status();
+}
+
+// out[t, out_off + i] = a[t, i] * gate(g[t, g_off + i]) * scale for i < width, in 32-bit, stored in the
+// compute dtype: the output gate of an attention layer whose attention ran in a kernel that knows no
+// gate.  gate_kind 0: none (scale and place only), 1: sigmoid, 2: silu.  `a` is contiguous [T, width]; g is float32 with `g_stride`
+// floats a row, out has `out_stride` elements a row.
+template <typename T>
+__global__ void gate_mul_kernel(const T* __restrict__ a, const float* __restrict__ g, long long g_stride, int g_off,
+                                T* __restrict__ out, long long out_stride, int out_off, int width, int gate_kind,
+                                float scale) {
+    pdl_begin();
+    const size_t t = blockIdx.y;
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < width; i += gridDim.x * blockDim.x) {
+        float gate = 1.0f;
+        if (gate_kind != 0) {
+            const float z = g[t * g_stride + g_off + i];
+            const float s = 1.0f / (1.0f + expf(-z));
+            gate = gate_kind == 2 ? z * s : s;
+        }
+        out[t * out_stride + out_off + i] = from_f32<T>(to_f32(a[t * width + i]) * gate * scale);
+    }
+}
+
+extern "C" int llm_gate_mul(const void* a, int dtype, const float* g, long long g_stride, int g_off, void* out,
+                            long long out_stride, int out_off, int num_tokens, int width, int gate_kind, float scale,
+                            uintptr_t stream) {
+    if (num_tokens <= 0) return LLM_OK;
+    if (width <= 0 || num_tokens > 65535 || gate_kind < 0 || gate_kind > 2 || (gate_kind && !g)) return LLM_REFUSED_SIZE;
+    const int threads = 256;
+    const int bx = (width + threads - 1) / threads;
+    const dim3 grid(bx < 64 ? bx : 64, num_tokens);
+    cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+    if (dtype == LLM_DT_F32)
+        launch_pdl((gate_mul_kernel<float>), grid, dim3(threads), 0, s, static_cast<const float*>(a), g, g_stride, g_off,
+                   static_cast<float*>(out), out_stride, out_off, width, gate_kind, scale);
+    else if (dtype == LLM_DT_BF16)
+        launch_pdl((gate_mul_kernel<bf16>), grid, dim3(threads), 0, s, static_cast<const bf16*>(a), g, g_stride, g_off,
+                   static_cast<bf16*>(out), out_stride, out_off, width, gate_kind, scale);
+    else
+        return LLM_REFUSED_DTYPE;
+    return launch_status();
+}

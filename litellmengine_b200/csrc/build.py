@@ -30,6 +30,8 @@ FAMILIES: Dict[str, List[str]] = {
     "activation": ["activation.cu"],
     "rope_cache": ["rope_cache.cu"],
     "attention_generic": ["attention_generic.cu"],
+    "attention_prepare": ["attention_prepare.cu"],
+    "linear_attention": ["linear_attention.cu"],
     "attention_decode": ["attention_decode.cu"],
     "attention_prefill": ["attention_prefill.cu"],
     "attention_prefill_tcgen05": ["attention_prefill_tcgen05.cu"],
@@ -84,6 +86,12 @@ _build_dir_cache = None
 
 
 def build_dir() -> str:
+    global _build_dir_cache
+    with _lock:                                   # families are built from several threads: probe the folders once
+        return _build_dir_locked()
+
+
+def _build_dir_locked() -> str:
     global _build_dir_cache
     if _build_dir_cache is None:
         env = os.environ.get("LITELLMENGINE_B200_BUILD_DIR")

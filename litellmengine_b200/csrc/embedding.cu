@@ -54,6 +54,64 @@ extern "C" int llm_embedding_gather(const int32_t* ids, const void* table, int t
     return launch_status();
 }
 
+// The same gather for designs that add a sinusoidal position vector to the token's row:
+//     out[t, 2i] = table[id, 2i] + sin(p * f_i),  out[t, 2i+1] = table[id, 2i+1] + cos(p * f_i)
+// with p the token's position and f_i = inv_freq[i] (a table in double precision made by the host, so
+// that the angle p * f_i is exact to the last bit of a float at any position).  The sum is 32-bit.
+// `copy` (optional) receives the same row in the compute dtype, for a first layer whose sublayers
+// read the stream itself instead of a norm of it.
+template <typename T, typename TC>
+__global__ void embedding_sinusoid_kernel(const int32_t* __restrict__ ids, const T* __restrict__ table,
+                                          float* __restrict__ out, TC* __restrict__ copy, int hidden, int vocab,
+                                          int32_t* __restrict__ status, const int32_t* __restrict__ feedback,
+                                          int feedback_len, const int32_t* __restrict__ positions,
+                                          const double* __restrict__ inv_freq) {
+    pdl_begin();
+    const int t = blockIdx.x;
+    int id = ids[t];
+    if (id < 0 && feedback != nullptr && -1 - id < feedback_len) id = feedback[-1 - id];
+    float* o = out + static_cast<size_t>(t) * hidden;
+    TC* c = copy ? copy + static_cast<size_t>(t) * hidden : nullptr;
+    const bool bad = id < 0 || id >= vocab;
+    if (bad && threadIdx.x == 0 && atomicCAS(status, 0, 1) == 0) status[1] = t;
+    const T* row = table + static_cast<size_t>(bad ? 0 : id) * hidden;
+    const double p = static_cast<double>(positions[t]);
+    for (int i = threadIdx.x; 2 * i < hidden; i += blockDim.x) {
+        double sn, cs;
+        sincos(p * inv_freq[i], &sn, &cs);
+        const float a = (bad ? 0.0f : to_f32(row[2 * i])) + static_cast<float>(sn);
+        o[2 * i] = a;
+        if (c) c[2 * i] = from_f32<TC>(a);
+        if (2 * i + 1 < hidden) {
+            const float b = (bad ? 0.0f : to_f32(row[2 * i + 1])) + static_cast<float>(cs);
+            o[2 * i + 1] = b;
+            if (c) c[2 * i + 1] = from_f32<TC>(b);
+        }
+    }
+}
+
+extern "C" int llm_embedding_sinusoid(const int32_t* ids, const void* table, int table_dtype, float* out, void* copy,
+                                      int copy_dtype, int num_tokens, int hidden, int vocab, int32_t* status,
+                                      const int32_t* feedback, int feedback_len, const int32_t* positions,
+                                      const double* inv_freq, uintptr_t stream) {
+    if (num_tokens <= 0) return LLM_OK;
+    if (hidden <= 0 || vocab <= 0) return LLM_REFUSED_SIZE;
+    const int threads = hidden >= 2048 ? 256 : 128;
+    cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+#define LAUNCH(T, TC)                                                                                          \
+    launch_pdl((embedding_sinusoid_kernel<T, TC>), dim3(num_tokens), dim3(threads), 0, s, ids,                 \
+               static_cast<const T*>(table), out, static_cast<TC*>(copy), hidden, vocab, status, feedback,     \
+               feedback_len, positions, inv_freq)
+    if (!copy) copy_dtype = LLM_DT_F32;
+    if (table_dtype == LLM_DT_F32 && copy_dtype == LLM_DT_F32) LAUNCH(float, float);
+    else if (table_dtype == LLM_DT_F32 && copy_dtype == LLM_DT_BF16) LAUNCH(float, bf16);
+    else if (table_dtype == LLM_DT_BF16 && copy_dtype == LLM_DT_F32) LAUNCH(bf16, float);
+    else if (table_dtype == LLM_DT_BF16 && copy_dtype == LLM_DT_BF16) LAUNCH(bf16, bf16);
+    else return LLM_REFUSED_DTYPE;
+#undef LAUNCH
+    return launch_status();
+}
+
 // dst[index[i]] = value[i] for i < *count (count lives on the device so that a captured
 // graph can replay with a different number of updates; a null count means max_count).  An index outside [0, dst_len)
 // is skipped and recorded in status.

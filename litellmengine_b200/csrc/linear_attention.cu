@@ -1,0 +1,291 @@
+// Gated linear attention: a per-head state S [D, V] that every token decays per key channel and
+// adds an outer product to,
+//
+//     S_t = diag(alpha_t) S_(t-1) + k_t v_t^T          o_t = S_t^T q_t
+//
+// with the state, the decays and every product of the recurrence in 32-bit CUDA-core arithmetic (the
+// recurrence's operands must not be rounded to 16 bits, so this is no tensor-core kernel; its roofline
+// is the float32 FMA rate for prompt portions and the state's bytes for single decoded tokens).
+//
+// gla_decay_kernel   ln(alpha)[t, c] = ln(sigmoid(z)) / tau,  z = w2[c, :] . a[t, :] + b2[c]: the second
+//                    half of a low-rank decay projection, kept out of the matrix-product path so that its
+//                    input is never rounded.
+// gla_scan_kernel    one block per (work item, head) walks the item's tokens in order.  Thread (dg, v)
+//                    keeps rows dg*R .. dg*R+R-1 of column v of the state in registers; tokens are
+//                    staged through shared memory sixteen at a time; the partial sums of o over the row
+//                    groups meet in shared memory (one barrier a token).  Epilogue per staged batch, a
+//                    warp per token: RMS norm of o over V, weight, output gate silu(g), scale, store in
+//                    the compute dtype into a column range of the layer's output buffer.
+//                    Three modes make long prompt portions parallel over chunks of tokens:
+//                      FULL   state in from the request's slot, outputs, state out to the slot
+//                             (single decoded tokens and short portions: one pass)
+//                      LOCAL  state in = 0, no outputs; the chunk's own contribution L and its total
+//                             decay A = prod alpha go to scratch
+//                      OUT    state in from scratch (what gla_chain_kernel put there), outputs only
+// gla_chain_kernel   per (long entry, head), over its chunks in order: scratch[c] <- S (the state that
+//                    enters chunk c), S <- diag(A_c) S + L_c; at the end the slot's state <- S.
+//
+// A position's output depends on how a prompt is cut only through the order of 32-bit additions.
+#include "common.cuh"
+
+#define GLA_TB 16          // tokens staged at a time
+#define GLA_FULL 0
+#define GLA_LOCAL 1
+#define GLA_OUT 2
+
+__global__ void gla_decay_kernel(const float* __restrict__ proj, long long stride, int a_off, int rank,
+                                 const float* __restrict__ w2, const float* __restrict__ b2, float inv_tau,
+                                 float* __restrict__ la, int channels) {
+    pdl_begin();
+    extern __shared__ float a[];                    // [rank]
+    const size_t t = blockIdx.x;
+    for (int j = threadIdx.x; j < rank; j += blockDim.x) a[j] = proj[t * stride + a_off + j];
+    __syncthreads();
+    for (int c = threadIdx.x; c < channels; c += blockDim.x) {
+        const float* w = w2 + static_cast<size_t>(c) * rank;
+        float z = b2 ? b2[c] : 0.0f;
+        for (int j = 0; j < rank; ++j) z += w[j] * a[j];
+        // ln(sigmoid(z)) without overflow on either side
+        const float ls = z < 0.0f ? z - log1pf(expf(z)) : -log1pf(expf(-z));
+        la[t * channels + c] = ls * inv_tau;
+    }
+}
+
+extern "C" int llm_gla_decay(const float* proj, long long stride, int a_off, int rank, const float* w2, const float* b2,
+                             float tau, float* la, int num_tokens, int channels, uintptr_t stream) {
+    if (num_tokens <= 0) return LLM_OK;
+    if (rank <= 0 || channels <= 0 || !(tau > 0.0f) || rank > 8192) return LLM_REFUSED_SIZE;
+    launch_pdl(gla_decay_kernel, dim3(num_tokens), dim3(channels >= 256 ? 256 : 128), rank * sizeof(float),
+               reinterpret_cast<cudaStream_t>(stream), proj, stride, a_off, rank, w2, b2, 1.0f / tau, la, channels);
+    return launch_status();
+}
+
+// items: int32 [n, 4] = (entry, first row in the batch, tokens, index of the item's scratch) or null: item i
+// is entry i, all of it.
+template <int R, typename TO>
+__global__ void gla_scan_kernel(
+    const float* __restrict__ proj, long long stride, int q_off, int k_off, int v_off, int g_off,
+    const float* __restrict__ la, const float* __restrict__ norm_w, float eps, float q_scale, float out_scale,
+    TO* __restrict__ out, long long out_stride, int out_off, float* __restrict__ state,
+    const int32_t* __restrict__ entry_slot, const int32_t* __restrict__ entry_q_start,
+    const int32_t* __restrict__ entry_q_len, const int32_t* __restrict__ items, int mode,
+    float* __restrict__ scratch_s, float* __restrict__ scratch_a, int H, int D, int V, int DG) {
+    pdl_begin();
+    extern __shared__ __align__(16) float smem[];
+    const int h = blockIdx.y;
+    int entry, row0, count, sidx;
+    if (items) {
+        entry = items[4 * blockIdx.x];
+        if (entry < 0) return;                       // padding of a work list
+        row0 = items[4 * blockIdx.x + 1];
+        count = items[4 * blockIdx.x + 2];
+        sidx = items[4 * blockIdx.x + 3];
+    } else {
+        entry = blockIdx.x;
+        row0 = entry_q_start[entry];
+        count = entry_q_len[entry];
+        sidx = entry;
+    }
+    const int tid = threadIdx.x, nthreads = blockDim.x;
+    // thread (dg, v) for tid < V * DG; the block is rounded up to whole warps and the rest only help to stage
+    const bool active = tid < V * DG;
+    const int v = active ? tid % V : 0, dg = active ? tid / V : 0;
+    float* sq = smem;                               // [TB][D]
+    float* sk = sq + GLA_TB * D;
+    float* sa = sk + GLA_TB * D;
+    float* sv = sa + GLA_TB * D;                    // [TB][V]
+    float* so = sv + GLA_TB * V;                    // [TB][V]
+    float* part = so + GLA_TB * V;                  // [2][DG][V]
+    const size_t HD = static_cast<size_t>(H) * D;
+
+    float S[R];
+    float* slot_state = state + (static_cast<size_t>(entry_slot[entry]) * H + h) * D * V;
+    const float* s_in = mode == GLA_FULL ? slot_state
+                        : (mode == GLA_OUT ? scratch_s + (static_cast<size_t>(sidx) * H + h) * D * V : nullptr);
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+        const int d = dg * R + r;
+        S[r] = (s_in && active && d < D) ? s_in[static_cast<size_t>(d) * V + v] : 0.0f;
+    }
+
+    for (int done = 0; done < count; done += GLA_TB) {
+        const int nb = min(GLA_TB, count - done);
+        const size_t base = static_cast<size_t>(row0 + done);
+        for (int idx = tid; idx < nb * D; idx += nthreads) {
+            const int tok = idx / D, d = idx - tok * D;
+            const float* pr = proj + (base + tok) * stride + h * D + d;
+            sk[idx] = pr[k_off];
+            sa[idx] = expf(la[(base + tok) * HD + h * D + d]);
+            if (mode != GLA_LOCAL) sq[idx] = pr[q_off] * q_scale;
+        }
+        for (int idx = tid; idx < nb * V; idx += nthreads) {
+            const int tok = idx / V, c = idx - tok * V;
+            sv[idx] = proj[(base + tok) * stride + v_off + h * V + c];
+        }
+        __syncthreads();
+        for (int tok = 0; tok < nb; ++tok) {
+            const float vt = sv[tok * V + v];
+            const float* a = sa + tok * D + dg * R;
+            const float* k = sk + tok * D + dg * R;
+            const float* q = sq + tok * D + dg * R;
+            float p0 = 0.0f, p1 = 0.0f;
+            if (mode == GLA_LOCAL) {
+#pragma unroll
+                for (int r = 0; r < R; ++r)
+                    if (active && dg * R + r < D) S[r] = a[r] * S[r] + k[r] * vt;
+            } else {
+#pragma unroll
+                for (int r = 0; r < R; r += 2) {
+                    if (active && dg * R + r < D) { S[r] = a[r] * S[r] + k[r] * vt; p0 += S[r] * q[r]; }
+                    if (active && dg * R + r + 1 < D) { S[r + 1] = a[r + 1] * S[r + 1] + k[r + 1] * vt; p1 += S[r + 1] * q[r + 1]; }
+                }
+                if (DG == 1) {
+                    if (active) so[tok * V + v] = p0 + p1;
+                } else {
+                    float* pp = part + (tok & 1) * DG * V;
+                    if (active) pp[dg * V + v] = p0 + p1;
+                    __syncthreads();
+                    if (active && dg == 0) {
+                        float o = 0.0f;
+                        for (int g2 = 0; g2 < DG; ++g2) o += pp[g2 * V + v];
+                        so[tok * V + v] = o;
+                    }
+                }
+            }
+        }
+        __syncthreads();
+        if (mode != GLA_LOCAL) {                    // a warp per token: norm over V, weight, gate, scale
+            const int warp = tid >> 5, lane = tid & 31, nwarps = nthreads >> 5;
+            for (int tok = warp; tok < nb; tok += nwarps) {
+                float ss = 0.0f;
+                for (int c = lane; c < V; c += 32) ss += so[tok * V + c] * so[tok * V + c];
+                ss = warp_sum(ss);
+                const float inv = 1.0f / sqrtf(ss / static_cast<float>(V) + eps);
+                const float* gr = proj + (base + tok) * stride + g_off + h * V;
+                TO* orow = out + (base + tok) * out_stride + out_off + h * V;
+                for (int c = lane; c < V; c += 32) {
+                    const float g = gr[c];
+                    const float silu = g / (1.0f + expf(-g));
+                    orow[c] = from_f32<TO>(so[tok * V + c] * inv * norm_w[c] * silu * out_scale);
+                }
+            }
+            __syncthreads();
+        }
+    }
+    if (mode == GLA_OUT) return;
+    float* s_out = mode == GLA_FULL ? slot_state : scratch_s + (static_cast<size_t>(sidx) * H + h) * D * V;
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+        const int d = dg * R + r;
+        if (active && d < D) s_out[static_cast<size_t>(d) * V + v] = S[r];
+    }
+    if (mode == GLA_LOCAL) {                        // the chunk's total decay per key channel
+        for (int d = tid; d < D; d += nthreads) {
+            float sum = 0.0f;
+            for (int tok = 0; tok < count; ++tok) sum += la[(static_cast<size_t>(row0) + tok) * HD + h * D + d];
+            scratch_a[(static_cast<size_t>(sidx) * H + h) * D + d] = expf(sum);
+        }
+    }
+}
+
+// Rows of a state column that one thread keeps (R), and the row groups DG = ceil(D / R): the smallest R
+// whose block of V * DG threads fits, first within 512 threads, then within what the kernel's registers
+// allow at that R (a block's registers are threads x registers per thread, at most 65,536).
+static int gla_rows_per_thread(int D, int V, int* dg_out) {
+    const int cands[4] = {8, 16, 32, 64};
+    const int limits[2][4] = {{512, 512, 512, 384}, {1024, 768, 640, 384}};
+    for (int pass = 0; pass < 2; ++pass)
+        for (int c = 0; c < 4; ++c) {
+            const int dg = (D + cands[c] - 1) / cands[c];
+            if (static_cast<long long>(V) * dg <= limits[pass][c]) {
+                *dg_out = dg;
+                return cands[c];
+            }
+        }
+    return 0;
+}
+
+extern "C" int llm_gla_supported(int D, int V) {
+    int dg;
+    return (D > 0 && V > 0 && gla_rows_per_thread(D, V, &dg) > 0) ? 1 : 0;
+}
+
+extern "C" int llm_gla_scan(
+    const float* proj, long long stride, int q_off, int k_off, int v_off, int g_off, const float* la,
+    const float* norm_w, float eps, float q_scale, float out_scale, void* out, int out_dtype, long long out_stride,
+    int out_off, float* state, const int32_t* entry_slot, const int32_t* entry_q_start, const int32_t* entry_q_len,
+    const int32_t* items, int num_items, int mode, float* scratch_s, float* scratch_a, int H, int D, int V,
+    uintptr_t stream) {
+    if (num_items <= 0) return LLM_OK;
+    if (H <= 0 || D <= 0 || V <= 0 || mode < 0 || mode > 2 || H > 65535) return LLM_REFUSED_SIZE;
+    if (mode != GLA_FULL && (!items || !scratch_s || !scratch_a)) return LLM_REFUSED_SIZE;
+    int DG = 0;
+    const int R = gla_rows_per_thread(D, V, &DG);
+    if (R == 0) return LLM_REFUSED_SIZE;
+    const size_t smem = (static_cast<size_t>(GLA_TB) * (3 * D + 2 * V) + 2 * static_cast<size_t>(DG) * V) * sizeof(float);
+    if (smem > 220 * 1024) return LLM_REFUSED_SIZE;
+    cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+    const dim3 grid(num_items, H), block((V * DG + 31) / 32 * 32);
+#define LAUNCH(RR, TO)                                                                                            \
+    do {                                                                                                          \
+        auto kern = gla_scan_kernel<RR, TO>;                                                                      \
+        if (smem > 48 * 1024) {                                                                                   \
+            const cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,         \
+                                                       static_cast<int>(smem));                                   \
+            if (e != cudaSuccess) return static_cast<int>(e);                                                     \
+        }                                                                                                         \
+        launch_pdl(kern, grid, block, smem, s, proj, stride, q_off, k_off, v_off, g_off, la, norm_w, eps, q_scale, \
+                   out_scale, static_cast<TO*>(out), out_stride, out_off, state, entry_slot, entry_q_start,       \
+                   entry_q_len, items, mode, scratch_s, scratch_a, H, D, V, DG);                                  \
+    } while (0)
+#define BY_R(TO)                                                                                                  \
+    switch (R) {                                                                                                  \
+        case 8: LAUNCH(8, TO); break;                                                                             \
+        case 16: LAUNCH(16, TO); break;                                                                           \
+        case 32: LAUNCH(32, TO); break;                                                                           \
+        default: LAUNCH(64, TO); break;                                                                           \
+    }
+    if (out_dtype == LLM_DT_F32) { BY_R(float) }
+    else if (out_dtype == LLM_DT_BF16) { BY_R(bf16) }
+    else return LLM_REFUSED_DTYPE;
+#undef BY_R
+#undef LAUNCH
+    return launch_status();
+}
+
+// chains: int32 [n, 3] = (entry, first scratch index, number of chunks); chunk c of the entry is scratch
+// index first + c.  grid (n, H, blocks over D*V).
+__global__ void gla_chain_kernel(float* __restrict__ state, float* __restrict__ scratch_s,
+                                 const float* __restrict__ scratch_a, const int32_t* __restrict__ chains,
+                                 const int32_t* __restrict__ entry_slot, int H, int D, int V) {
+    pdl_begin();
+    const int entry = chains[3 * blockIdx.x];
+    if (entry < 0) return;
+    const int first = chains[3 * blockIdx.x + 1], n = chains[3 * blockIdx.x + 2];
+    const int h = blockIdx.y;
+    const int e = blockIdx.z * blockDim.x + threadIdx.x;
+    if (e >= D * V) return;
+    const int d = e / V;
+    float* st = state + (static_cast<size_t>(entry_slot[entry]) * H + h) * D * V + e;
+    float S = *st;
+    for (int c = 0; c < n; ++c) {
+        const size_t at = static_cast<size_t>(first + c) * H + h;
+        float* cell = scratch_s + at * D * V + e;
+        const float L = *cell;
+        *cell = S;
+        S = scratch_a[at * D + d] * S + L;
+    }
+    *st = S;
+}
+
+extern "C" int llm_gla_chain(float* state, float* scratch_s, const float* scratch_a, const int32_t* chains,
+                             int num_chains, const int32_t* entry_slot, int H, int D, int V, uintptr_t stream) {
+    if (num_chains <= 0) return LLM_OK;
+    if (H <= 0 || D <= 0 || V <= 0 || H > 65535) return LLM_REFUSED_SIZE;
+    const int threads = 256;
+    const int bz = (D * V + threads - 1) / threads;
+    if (bz > 65535) return LLM_REFUSED_SIZE;
+    launch_pdl(gla_chain_kernel, dim3(num_chains, H, bz), dim3(threads), 0, reinterpret_cast<cudaStream_t>(stream),
+               state, scratch_s, scratch_a, chains, entry_slot, H, D, V);
+    return launch_status();
+}

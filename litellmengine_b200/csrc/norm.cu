@@ -129,3 +129,62 @@ extern "C" int llm_rmsnorm(void* x, int x_dtype, const void* delta, int delta_dt
 #undef CASE
     return LLM_REFUSED_DTYPE;
 }
+
+// A norm on a sublayer's OUTPUT, fused with the residual add that follows it:
+//     h[row] += y[row] * rsqrt(mean(y[row]^2) + eps) * w          (32-bit throughout; h is float32)
+// and, optionally, `copy[row]` = the new h[row] in the compute dtype: what the next sublayer of a
+// design reads whose sublayers take the stream itself (no norm in front of them).
+// One block per row; y is float32 or bfloat16, `y_stride` elements from row to row.
+template <typename TY, typename TC>
+__global__ void rmsnorm_add_kernel(float* __restrict__ h, const TY* __restrict__ y, long long y_stride,
+                                   const float* __restrict__ w, TC* __restrict__ copy, int hidden, float eps) {
+    pdl_begin();
+    extern __shared__ __align__(16) float smem[];
+    float* v = smem;
+    float* scratch = smem + ((hidden + 7) & ~7);
+    const TY* yr = y + static_cast<size_t>(blockIdx.x) * y_stride;
+    float* hr = h + static_cast<size_t>(blockIdx.x) * hidden;
+    TC* cr = copy ? copy + static_cast<size_t>(blockIdx.x) * hidden : nullptr;
+    float ss = 0.0f;
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+        const float a = to_f32(yr[i]);
+        v[i] = a;
+        ss += a * a;
+    }
+    const float total = block_sum(ss, scratch);
+    const float inv = 1.0f / sqrtf(total / static_cast<float>(hidden) + eps);
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+        const float a = hr[i] + v[i] * inv * w[i];
+        hr[i] = a;
+        if (cr) cr[i] = from_f32<TC>(a);
+    }
+}
+
+extern "C" int llm_rmsnorm_add(float* h, const void* y, int y_dtype, long long y_stride, const float* w, void* copy,
+                               int copy_dtype, int num_rows, int hidden, float eps, uintptr_t stream) {
+    if (num_rows <= 0) return LLM_OK;
+    if (hidden <= 0 || y_stride < hidden) return LLM_REFUSED_SIZE;
+    const size_t smem = (static_cast<size_t>((hidden + 7) & ~7) + 33) * sizeof(float);
+    if (smem > 200 * 1024) return LLM_REFUSED_SIZE;
+    const int threads = hidden >= 4096 ? 512 : (hidden >= 1024 ? 256 : 128);
+    cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+    if (!copy) copy_dtype = LLM_DT_F32;
+#define LAUNCH(TY, TC)                                                                                           \
+    do {                                                                                                         \
+        auto kern = rmsnorm_add_kernel<TY, TC>;                                                                  \
+        if (smem > 48 * 1024) {                                                                                  \
+            const cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,        \
+                                                       static_cast<int>(smem));                                  \
+            if (e != cudaSuccess) return static_cast<int>(e);                                                    \
+        }                                                                                                        \
+        launch_pdl(kern, dim3(num_rows), dim3(threads), smem, s, h, static_cast<const TY*>(y), y_stride, w,      \
+                   static_cast<TC*>(copy), hidden, eps);                                                         \
+    } while (0)
+    if (y_dtype == LLM_DT_F32 && copy_dtype == LLM_DT_F32) LAUNCH(float, float);
+    else if (y_dtype == LLM_DT_F32 && copy_dtype == LLM_DT_BF16) LAUNCH(float, bf16);
+    else if (y_dtype == LLM_DT_BF16 && copy_dtype == LLM_DT_F32) LAUNCH(bf16, float);
+    else if (y_dtype == LLM_DT_BF16 && copy_dtype == LLM_DT_BF16) LAUNCH(bf16, bf16);
+    else return LLM_REFUSED_DTYPE;
+#undef LAUNCH
+    return launch_status();
+}

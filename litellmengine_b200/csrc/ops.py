@@ -157,6 +157,29 @@ def embedding(ids: torch.Tensor, table: torch.Tensor, status: torch.Tensor,
     return out
 
 
+def embedding_sinusoid(ids: torch.Tensor, table: torch.Tensor, positions: torch.Tensor, inv_freq: torch.Tensor,
+                       status: torch.Tensor, feedback: Optional[torch.Tensor] = None,
+                       copy_dtype: Optional[torch.dtype] = None):
+    """float32 [T, H] = table[ids] + the sinusoidal vector of each token's position (entry 2i: sin(p * f_i),
+    entry 2i+1: cos(p * f_i), f = `inv_freq`, float64 [ceil(H/2)]).  With `copy_dtype` the same rows come back a
+    second time in that dtype.  Returns (stream, copy or None)."""
+    _dev(ids, table, positions, inv_freq, status, feedback)
+    _i32(ids, "ids")
+    _i32(positions, "positions")
+    T, (V, H) = ids.numel(), table.shape
+    if inv_freq.dtype != torch.float64 or inv_freq.numel() != (H + 1) // 2:
+        raise KernelError("inv_freq must be float64 [ceil(hidden/2)]")
+    out = torch.empty((T, H), dtype=torch.float32, device=table.device)
+    copy = torch.empty((T, H), dtype=copy_dtype, device=table.device) if copy_dtype is not None else None
+    f = _fn("embedding", "llm_embedding_sinusoid",
+            [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_int,
+             c_void_p, c_void_p, c_void_p])
+    _check(f(_ptr(ids), _ptr(table), _dt(table), _ptr(out), _ptr(copy), _dt(copy) if copy is not None else 0, T, H, V,
+             _ptr(status), _ptr(feedback), feedback.numel() if feedback is not None else 0, _ptr(positions),
+             _ptr(inv_freq), _stream()), "embedding_sinusoid")
+    return out, copy
+
+
 def scatter_int32(dst: torch.Tensor, index: torch.Tensor, value: torch.Tensor, count: torch.Tensor,
                   max_count: int, status: torch.Tensor) -> None:
     """dst.flat[index[i]] = value[i] for i < count[0] (count is a device scalar; None: for i < max_count)."""
@@ -194,6 +217,25 @@ def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out_dtype: torch.
     _check(f(_ptr(x), _dt(x), _ptr(delta), _dt(delta) if delta is not None else 0, _ptr(weight), _ptr(out),
              _dt(out), _ptr(rows), n, H, float(eps), 1 if write_sum else 0, parts, part_stride, _stream()), "rmsnorm")
     return out
+
+
+def rmsnorm_add(h: torch.Tensor, y: torch.Tensor, weight: torch.Tensor, eps: float,
+                copy_dtype: Optional[torch.dtype] = None) -> Optional[torch.Tensor]:
+    """h (float32, in place) += rmsnorm(y) * weight, row by row: a norm on a sublayer's output joined with
+    the residual add.  With `copy_dtype`, returns the new h in that dtype (what the next sublayer reads)."""
+    y = as_tensor(y)
+    _dev(h, weight)
+    if not y.is_cuda or y.dim() != 2 or y.stride(1) != 1:
+        raise KernelError("y must be a CUDA matrix with unit stride along its rows")
+    T, H = h.shape
+    if h.dtype != torch.float32 or tuple(y.shape) != (T, H) or weight.dtype != torch.float32 or weight.numel() != H:
+        raise KernelError("rmsnorm_add wants a float32 stream, a y of its shape and a float32 weight of the row length")
+    copy = torch.empty((T, H), dtype=copy_dtype, device=h.device) if copy_dtype is not None else None
+    f = _fn("norm", "llm_rmsnorm_add",
+            [c_void_p, c_void_p, c_int, c_longlong, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_void_p])
+    _check(f(_ptr(h), _ptr(y), _dt(y), y.stride(0), _ptr(weight), _ptr(copy), _dt(copy) if copy is not None else 0,
+             T, H, float(eps), _stream()), "rmsnorm_add")
+    return copy
 
 
 def silu_and_mul(gate_up, out: Optional[torch.Tensor] = None) -> torch.Tensor:
@@ -368,6 +410,162 @@ def paged_attention_generic(q: torch.Tensor, cache: torch.Tensor, positions, tok
              int(window) if window else 0, float(scale), cache.shape[0], _ptr(status), _stream()),
            "paged_attention_generic")
     return out
+
+
+NORM_SCOPES = {None: 0, "none": 0, "head": 1, "projection": 2}
+
+
+def attention_prepare(proj: torch.Tensor, q_off: int, k_off: int, v_off: int, biases, q_norm_w, k_norm_w,
+                      norm_scope, eps: float, temperature, keys: Optional[torch.Tensor],
+                      values: Optional[torch.Tensor], positions, token_entry, entry_slot,
+                      block_table: Optional[torch.Tensor], nq: int, nkv: int, dk: int, dv: int, page_size: int,
+                      status: torch.Tensor, q_dtype: torch.dtype) -> torch.Tensor:
+    """From a float32 projection [T, n] whose columns hold q (from q_off), k (from k_off) and v (from v_off):
+    add the biases (`biases` = (bq, bk, bv), any of them None), normalise q and k in 32-bit (`norm_scope`
+    'head': each head by itself with a weight [dk]; 'projection': all heads of a token together with a
+    weight over the whole projection; None), multiply q by the query temperature 1 + coef * ln(floor((p + 1)
+    / every) + 1) (`temperature` = (coef, every) or None), return q [T, nq*dk] in `q_dtype` and write k and
+    v into the token's place in `keys` [pages, nkv, page, dk] and `values` [pages, nkv, page, dv] (views
+    with any page stride).  keys None: a mixer that writes no keys and values."""
+    if proj.dtype != torch.float32 or proj.dim() != 2 or proj.stride(1) != 1 or not proj.is_cuda:
+        raise KernelError("proj must be a float32 CUDA matrix with unit stride along its rows")
+    bq, bk, bv = biases if biases is not None else (None, None, None)
+    _dev(bq, bk, bv, q_norm_w, k_norm_w, positions, token_entry, entry_slot, block_table, status)
+    T, n = proj.shape
+    if max(q_off + nq * dk, (k_off + nkv * dk) if keys is not None else 0, (v_off + nkv * dv) if keys is not None else 0) > n:
+        raise KernelError("the projection is narrower than its q, k and v pieces")
+    scope = NORM_SCOPES[norm_scope]
+    for w, size in ((q_norm_w, nq * dk if scope == 2 else dk), (k_norm_w, nkv * dk if scope == 2 else dk)):
+        if w is not None and (w.dtype != torch.float32 or w.numel() != size):
+            raise KernelError(f"a q/k norm weight must be float32 [{size}]")
+    for b, size in ((bq, nq * dk), (bk, nkv * dk), (bv, nkv * dv)):
+        if b is not None and (b.dtype != torch.float32 or b.numel() != size):
+            raise KernelError(f"a projection bias must be float32 [{size}]")
+    kps = vps = pages = 0
+    if keys is not None:
+        for c, w in ((keys, dk), (values, dv)):
+            if (c is None or not c.is_cuda or c.dim() != 4 or tuple(c.shape[1:]) != (nkv, page_size, w)
+                    or c[0].stride() != (page_size * w, w, 1)):
+                raise KernelError("keys / values must be [pages, kv_heads, page_size, width] with dense pages")
+        if keys.dtype != values.dtype or block_table is None:
+            raise KernelError("keys and values must share a dtype and come with a block table")
+        kps, vps, pages = keys.stride(0), values.stride(0), keys.shape[0]
+    coef, every = (float(temperature[0]), int(temperature[1])) if temperature is not None else (0.0, 0)
+    q = torch.empty((T, nq * dk), dtype=q_dtype, device=proj.device)
+    f = _fn("attention_prepare", "llm_attention_prepare",
+            [c_void_p, c_longlong, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_float,
+             c_float, c_int, c_void_p, c_int, c_void_p, c_void_p, c_int, c_longlong, c_longlong, c_void_p, c_void_p,
+             c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p])
+    _check(f(_ptr(proj), proj.stride(0), q_off, k_off, v_off, _ptr(bq), _ptr(bk), _ptr(bv), _ptr(q_norm_w),
+             _ptr(k_norm_w), scope, float(eps), coef, every, _ptr(q), _dt(q), _ptr(keys), _ptr(values),
+             _dt(keys) if keys is not None else 0, kps, vps, _ptr(positions), _ptr(token_entry), _ptr(entry_slot),
+             _ptr(block_table), block_table.shape[1] if block_table is not None else 0, T, nq, nkv, dk, dv, page_size,
+             pages, _ptr(status), _stream()), "attention_prepare")
+    return q
+
+
+def gate_mul(a: torch.Tensor, gate: Optional[torch.Tensor], gate_off: int, out: torch.Tensor, out_off: int,
+             kind: Optional[str], scale: float = 1.0) -> None:
+    """out[:, out_off : out_off + w] = a * gate_fn(gate[:, gate_off : gate_off + w]) * scale for a contiguous
+    a [T, w]; gate is float32; `kind` 'sigmoid', 'silu' or None (no gate: scale and place only)."""
+    _dev(a)
+    T, w = a.shape
+    if kind is None:
+        gate = None
+    if (gate is not None and (gate.dtype != torch.float32 or gate.stride(1) != 1)) or out.stride(1) != 1 or out.dtype != a.dtype:
+        raise KernelError("gate must be float32, out of a's dtype, both with unit stride along rows")
+    f = _fn("attention_prepare", "llm_gate_mul",
+            [c_void_p, c_int, c_void_p, c_longlong, c_int, c_void_p, c_longlong, c_int, c_int, c_int, c_int, c_float, c_void_p])
+    _check(f(_ptr(a), _dt(a), _ptr(gate), gate.stride(0) if gate is not None else 0, gate_off, _ptr(out), out.stride(0),
+             out_off, T, w, {None: 0, "sigmoid": 1, "silu": 2}[kind], float(scale), _stream()), "gate_mul")
+
+
+def paged_attention_generic_kv(q: torch.Tensor, keys: torch.Tensor, values: torch.Tensor, positions, token_entry,
+                               entry_slot, block_table: torch.Tensor, nq: int, nkv: int, dk: int, dv: int,
+                               page_size: int, window: Optional[int], scale: float, status: torch.Tensor,
+                               out: torch.Tensor, out_off: int = 0, gate: Optional[torch.Tensor] = None,
+                               gate_off: int = 0, out_scale: float = 1.0) -> torch.Tensor:
+    """Causal attention of every token in q [T, nq*dk] over its request's pages of `keys` [pages, nkv, page,
+    dk] and `values` [pages, nkv, page, dv] (views with any page stride), written into columns out_off ..
+    out_off + nq*dv of `out`, times sigmoid(gate[:, gate_off + ...]) (float32, optional) and `out_scale`."""
+    _dev(q, positions, token_entry, entry_slot, block_table, status)
+    T = q.shape[0]
+    for c, w in ((keys, dk), (values, dv)):
+        if (not c.is_cuda or c.dim() != 4 or tuple(c.shape[1:]) != (nkv, page_size, w)
+                or c[0].stride() != (page_size * w, w, 1)):
+            raise KernelError("keys / values must be [pages, kv_heads, page_size, width] with dense pages")
+    if q.shape[1] != nq * dk or out.dtype != q.dtype or out.stride(1) != 1 or out.shape[0] != T:
+        raise KernelError("q must be [T, heads*dk] and out a matrix of q's dtype with T rows")
+    if gate is not None and (gate.dtype != torch.float32 or gate.stride(1) != 1):
+        raise KernelError("gate must be float32 with unit stride along rows")
+    f = _fn("attention_generic", "llm_paged_attention_generic_kv",
+            [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_longlong, c_longlong, c_void_p, c_void_p, c_void_p,
+             c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_longlong,
+             c_int, c_float, c_longlong, c_int, c_void_p, c_void_p])
+    _check(f(_ptr(q), _ptr(out), _dt(q), _ptr(keys), _ptr(values), _dt(keys), keys.stride(0), values.stride(0),
+             _ptr(positions), _ptr(token_entry), _ptr(entry_slot), _ptr(block_table), block_table.shape[1], T, nq, nkv,
+             dk, dv, page_size, int(window) if window else 0, float(scale), keys.shape[0], _ptr(gate),
+             gate.stride(0) if gate is not None else 0, gate_off, float(out_scale), out.stride(0), out_off,
+             _ptr(status), _stream()), "paged_attention_generic_kv")
+    return out
+
+
+# ---- gated linear attention ------------------------------------------------------------------
+GLA_FULL, GLA_LOCAL, GLA_OUT = 0, 1, 2
+
+
+def gla_supported(d: int, v: int) -> bool:
+    return bool(_fn("linear_attention", "llm_gla_supported", [c_int, c_int])(d, v))
+
+
+def gla_decay(proj: torch.Tensor, a_off: int, rank: int, w2: torch.Tensor, b2: Optional[torch.Tensor],
+              tau: float) -> torch.Tensor:
+    """ln(alpha) = ln(sigmoid(proj[:, a_off : a_off + rank] @ w2^T + b2)) / tau as float32 [T, channels]."""
+    _dev(w2, b2)
+    if proj.dtype != torch.float32 or proj.stride(1) != 1 or w2.dtype != torch.float32 or w2.shape[1] != rank:
+        raise KernelError("gla_decay wants a float32 projection and a float32 w2 [channels, rank]")
+    T, C = proj.shape[0], w2.shape[0]
+    la = torch.empty((T, C), dtype=torch.float32, device=proj.device)
+    f = _fn("linear_attention", "llm_gla_decay",
+            [c_void_p, c_longlong, c_int, c_int, c_void_p, c_void_p, c_float, c_void_p, c_int, c_int, c_void_p])
+    _check(f(_ptr(proj), proj.stride(0), a_off, rank, _ptr(w2), _ptr(b2), float(tau), _ptr(la), T, C, _stream()),
+           "gla_decay")
+    return la
+
+
+def gla_scan(proj: torch.Tensor, offs, la: torch.Tensor, norm_w: torch.Tensor, eps: float, q_scale: float,
+             out_scale: float, out: torch.Tensor, out_off: int, state: torch.Tensor, entry_slot, entry_q_start,
+             entry_q_len, items: Optional[torch.Tensor], num_items: int, mode: int,
+             scratch_s: Optional[torch.Tensor], scratch_a: Optional[torch.Tensor], H: int, D: int, V: int) -> None:
+    """The recurrence S <- diag(alpha) S + k v^T, o = S^T q over the tokens of each work item, per head, with
+    the per-head RMS norm of o (weight `norm_w` [V]), the silu output gate and `out_scale` applied before
+    the store into columns out_off .. out_off + H*V of `out`.  `offs` = (q, k, v, g) column offsets in the
+    float32 projection; `state` float32 [slots, H, D, V]; see csrc/linear_attention.cu for the modes."""
+    _dev(la, norm_w, state, entry_slot, entry_q_start, entry_q_len, items, scratch_s, scratch_a)
+    if (proj.dtype != torch.float32 or proj.stride(1) != 1 or la.dtype != torch.float32 or state.dtype != torch.float32
+            or tuple(state.shape[1:]) != (H, D, V) or norm_w.dtype != torch.float32 or norm_w.numel() != V
+            or out.stride(1) != 1):
+        raise KernelError("gla_scan: float32 projection, decays and state [slots, H, D, V]; norm weight [V]")
+    q_off, k_off, v_off, g_off = offs
+    f = _fn("linear_attention", "llm_gla_scan",
+            [c_void_p, c_longlong, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_float, c_float, c_float, c_void_p,
+             c_int, c_longlong, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p,
+             c_void_p, c_int, c_int, c_int, c_void_p])
+    _check(f(_ptr(proj), proj.stride(0), q_off, k_off, v_off, g_off, _ptr(la), _ptr(norm_w), float(eps),
+             float(q_scale), float(out_scale), _ptr(out), _dt(out), out.stride(0), out_off, _ptr(state),
+             _ptr(entry_slot), _ptr(entry_q_start), _ptr(entry_q_len), _ptr(items), num_items, mode,
+             _ptr(scratch_s), _ptr(scratch_a), H, D, V, _stream()), "gla_scan")
+
+
+def gla_chain(state: torch.Tensor, scratch_s: torch.Tensor, scratch_a: torch.Tensor, chains: torch.Tensor,
+              num_chains: int, entry_slot, H: int, D: int, V: int) -> None:
+    """Per (chain, head): walk the chain's chunks in order, leaving in scratch_s[c] the state that enters
+    chunk c and in the request's slot the state after the last one."""
+    _dev(state, scratch_s, scratch_a, chains, entry_slot)
+    f = _fn("linear_attention", "llm_gla_chain",
+            [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_void_p])
+    _check(f(_ptr(state), _ptr(scratch_s), _ptr(scratch_a), _ptr(chains), num_chains, _ptr(entry_slot), H, D, V,
+             _stream()), "gla_chain")
 
 
 def fast_attention_supported(d: int, group: int) -> bool:

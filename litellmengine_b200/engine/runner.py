@@ -72,8 +72,7 @@ class ModelRunner:
         # captured the second time that size is seen.  Only for models whose parts all say
         # they launch nothing but kernels on the current stream (no host reads, no host loops).
         self.use_graphs = use_graphs and all(
-            getattr(b.mixer, "graph_safe", False) and getattr(b.feed_forward, "graph_safe", False)
-            for b in model.blocks)
+            getattr(part, "graph_safe", False) for b in model.blocks for part in b.parts())
         self._graphs = {}
         self._mixed_graphs = True               # graphs for steps that are not all single decoded tokens
         # Parts that say `any_division_safe` read the step's per-entry arrays only through kernels that
@@ -81,8 +80,7 @@ class ModelRunner:
         # Parts that are only `graph_safe` may shape tensors by the number of entries, so their graphs
         # are kept per (tokens, entries).
         self._entries_free = all(
-            getattr(b.mixer, "any_division_safe", False) and getattr(b.feed_forward, "any_division_safe", False)
-            for b in model.blocks)
+            getattr(part, "any_division_safe", False) for b in model.blocks for part in b.parts())
         self._mixed_count = 0
         self._graph_seen = {}
         self._graph_pool = None

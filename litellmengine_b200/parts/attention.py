@@ -187,6 +187,142 @@ class AttentionMixer:
         return ops.linear(a, self.w_o, out_dtype=torch.float32, partials_ok=getattr(ctx, "partials_ok", False))
 
 
+class BranchMixer:
+    """What a mixer offers so that it can stand alone or beside others under `ParallelMixer`: after
+    `load`, `w_in` [in_width, hidden] (every projection of the layer input it wants, as one matrix) and
+    `w_o` [hidden, out_width]; `mix` reads its columns of a float32 projection and writes its columns of
+    the layer's output buffer, which `w_o` then maps to the hidden size.  Standing alone that is three
+    steps; a parent that runs several branches fuses their `w_in` into one product and their `w_o`
+    into another and calls `mix` of each on its own column ranges."""
+
+    in_width = 0
+    out_width = 0
+    w_in: Optional[torch.Tensor] = None
+    w_o: Optional[torch.Tensor] = None
+
+    def mix(self, proj: torch.Tensor, col0: int, ctx: StageContext, out: torch.Tensor, out_col0: int,
+            out_scale: float) -> None:
+        raise NotImplementedError
+
+    def forward(self, x: torch.Tensor, ctx: StageContext):
+        proj = ops.linear(x, self.w_in, out_dtype=torch.float32)
+        out = torch.empty((x.shape[0], self.out_width), dtype=self.dtype, device=x.device)
+        self.mix(proj, 0, ctx, out, 0, 1.0)
+        return ops.linear(out, self.w_o, out_dtype=torch.float32, partials_ok=getattr(ctx, "partials_ok", False))
+
+    def fused_by_parent(self) -> None:
+        """A parent holds the fused matrices now; the branch keeps no copies."""
+        self.w_in = self.w_o = None
+
+
+@register_mixer("gated_attention")
+class GatedAttentionMixer(BranchMixer):
+    """Grouped-query causal softmax attention over the paged cache with the options of `MixerSpec`:
+    values of their own width, biased q/k/v projections, a q/k norm per head or over the token's whole
+    projection, a query temperature q *= 1 + coef * ln(floor((p + 1) / every) + 1), and an output gate
+    sigmoid(W_g x) on the concatenated heads before the output projection.  No rotation: a model that
+    uses this mixer encodes positions elsewhere.  One product yields [q | k | v | g] per token in
+    float32; one kernel adds the biases, normalises, applies the temperature and writes keys and values
+    to their pages; the attention kernel applies the gate as it stores."""
+
+    graph_safe = True
+    any_division_safe = True
+
+    _DEFAULT_NAMES = {"q": "q_proj.weight", "k": "k_proj.weight", "v": "v_proj.weight", "g": "g_proj.weight",
+                      "o": "o_proj.weight", "q_bias": "q_proj.bias", "k_bias": "k_proj.bias", "v_bias": "v_proj.bias",
+                      "q_norm": "q_norm.weight", "k_norm": "k_norm.weight"}
+
+    def __init__(self, spec: MixerSpec, hidden_size: int, compute_dtype: torch.dtype, device):
+        if spec.num_heads <= 0 or spec.num_kv_heads <= 0 or spec.num_heads % spec.num_kv_heads:
+            raise ValueError("attention heads must be a positive multiple of kv heads")
+        self.dv = spec.value_dim or spec.head_dim
+        if not 0 < spec.head_dim <= 256 or not 0 < self.dv <= 256:
+            raise ValueError("key and value widths must be between 1 and 256")
+        if spec.position.kind != "none":
+            raise ValueError("the gated attention mixer applies no position encoding of its own")
+        if spec.qk_norm_scope not in ("head", "projection"):
+            raise ValueError(f"qk_norm_scope {spec.qk_norm_scope!r}: 'head' or 'projection'")
+        if spec.output_gate not in (None, "sigmoid"):
+            raise ValueError(f"output_gate {spec.output_gate!r}: 'sigmoid' or None")
+        if not spec.has_kv:
+            raise ValueError("the gated attention mixer keeps its own keys and values")
+        self.spec, self.hidden, self.dtype, self.device = spec, hidden_size, compute_dtype, torch.device(device)
+        self.nq, self.nkv, self.d = spec.num_heads, spec.num_kv_heads, spec.head_dim
+        self.scale = spec.scale if spec.scale is not None else 1.0 / math.sqrt(float(self.d))
+        self.names = dict(self._DEFAULT_NAMES, **dict(spec.tensor_names))
+        self.q_off, self.k_off = 0, self.nq * self.d
+        self.v_off = self.k_off + self.nkv * self.d
+        self.g_off = self.v_off + self.nkv * self.dv
+        self.in_width = self.g_off + (self.nq * self.dv if spec.output_gate else 0)
+        self.out_width = self.nq * self.dv
+        self.biases = None
+        self.q_norm_w = self.k_norm_w = None
+        # the tuned bfloat16 kernels read keys and values of one width from one tensor
+        self._tuned = (compute_dtype == torch.bfloat16 and self.dv == self.d and self.device.type == "cuda"
+                       and ops.fast_attention_supported(self.d, self.nq // self.nkv))
+
+    def parameters(self) -> Dict[str, ParamSpec]:
+        n, s = self.names, self.spec
+        p = {n["q"]: ParamSpec((self.nq * self.d, self.hidden)), n["k"]: ParamSpec((self.nkv * self.d, self.hidden)),
+             n["v"]: ParamSpec((self.nkv * self.dv, self.hidden)), n["o"]: ParamSpec((self.hidden, self.nq * self.dv))}
+        if s.output_gate:
+            p[n["g"]] = ParamSpec((self.nq * self.dv, self.hidden))
+        if s.bias:
+            for key, size in (("q_bias", self.nq * self.d), ("k_bias", self.nkv * self.d), ("v_bias", self.nkv * self.dv)):
+                p[n[key]] = ParamSpec((size,), role="scale", init=("normal", 0.02))
+        if s.qk_norm is not None:
+            whole = s.qk_norm_scope == "projection"
+            p[n["q_norm"]] = ParamSpec((self.nq * self.d if whole else self.d,), role="scale", init=("one_plus_normal", 0.01))
+            p[n["k_norm"]] = ParamSpec((self.nkv * self.d if whole else self.d,), role="scale", init=("one_plus_normal", 0.01))
+        return p
+
+    def load(self, t: Dict[str, torch.Tensor]) -> None:
+        n, s = self.names, self.spec
+        rows = [t[n["q"]], t[n["k"]], t[n["v"]]] + ([t[n["g"]]] if s.output_gate else [])
+        dt = torch.float32 if any(x.dtype == torch.float32 for x in rows) else rows[0].dtype
+        self.w_in = torch.cat([x.to(dt) for x in rows], dim=0).contiguous()
+        self.w_o = t[n["o"]].contiguous()
+        if s.bias:
+            self.biases = tuple(t[n[k]].contiguous() for k in ("q_bias", "k_bias", "v_bias"))
+        if s.qk_norm is not None:
+            self.q_norm_w, self.k_norm_w = t[n["q_norm"]].contiguous(), t[n["k_norm"]].contiguous()
+        ops.prepare_streaming(self.w_in)
+        ops.prepare_streaming(self.w_o)
+
+    def cache_need(self):
+        return PagedNeed(self.nkv, self.d, self.spec.window, None if self.dv == self.d else self.dv)
+
+    def step_prelude(self):
+        return AttentionWork() if self._tuned else None
+
+    @property
+    def graph_variant_group(self):
+        return ("attention", self.nkv) if self._tuned else ("gated_attention",)
+
+    def graph_variant(self, batch, padded: bool) -> int:
+        if not self._tuned:
+            return 0
+        return AttentionMixer.graph_variant(self, batch, padded)
+
+    def mix(self, proj, col0, ctx, out, out_col0, out_scale):
+        b, s = ctx.batch, self.spec
+        if not ctx.writes_cache:
+            raise RuntimeError("a mixer with its own keys and values was given a borrowed cache")
+        q = ops.attention_prepare(
+            proj, col0 + self.q_off, col0 + self.k_off, col0 + self.v_off, self.biases, self.q_norm_w, self.k_norm_w,
+            s.qk_norm_scope if s.qk_norm is not None else None, s.qk_norm.eps if s.qk_norm is not None else 0.0,
+            s.query_temperature, ctx.cache_keys, ctx.cache_values, b.positions, b.token_entry, b.entry_slot,
+            ctx.block_table, self.nq, self.nkv, self.d, self.dv, ctx.page_size, ctx.status, self.dtype)
+        if self._tuned and ctx.cache is not None and b.preludes.get(AttentionWork.name) is not None:
+            a = attention_over_pages(q, ctx, self.nq, self.nkv, self.d, s.window, self.scale)
+            ops.gate_mul(a, proj, col0 + self.g_off, out, out_col0, s.output_gate, out_scale)
+            return
+        ops.paged_attention_generic_kv(
+            q, ctx.cache_keys, ctx.cache_values, b.positions, b.token_entry, b.entry_slot, ctx.block_table, self.nq,
+            self.nkv, self.d, self.dv, ctx.page_size, s.window, self.scale, ctx.status, out, out_col0,
+            gate=proj if s.output_gate else None, gate_off=col0 + self.g_off, out_scale=out_scale)
+
+
 _slots = {}
 
 

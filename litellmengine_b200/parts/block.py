@@ -20,26 +20,39 @@ class Block:
         self.mixer_norm = lookup("norm", spec.mixer_norm.kind)(spec.mixer_norm, hidden_size)
         self.feed_forward_norm = lookup("norm", spec.feed_forward_norm.kind)(spec.feed_forward_norm, hidden_size)
         self.mixer = lookup("mixer", spec.mixer.kind)(spec.mixer, hidden_size, compute_dtype, device)
-        self.feed_forward = lookup("feed_forward", spec.feed_forward.kind)(
-            spec.feed_forward, hidden_size, compute_dtype, device)
+        # a layer may be its mixer only: then it has no feed-forward and no norm for one
+        self.feed_forward = None
+        if spec.feed_forward is not None:
+            self.feed_forward = lookup("feed_forward", spec.feed_forward.kind)(
+                spec.feed_forward, hidden_size, compute_dtype, device)
+        else:
+            self.feed_forward_norm = None
         self.arrangement = lookup("arrangement", spec.arrangement)
 
     def _children(self):
         s = self.spec
-        return ((s.mixer_norm_name, self.mixer_norm), (s.mixer.weight_prefix, self.mixer),
-                (s.feed_forward_norm_name, self.feed_forward_norm),
-                (s.feed_forward.weight_prefix, self.feed_forward))
+        out = [(s.mixer_norm_name, self.mixer_norm), (s.mixer.weight_prefix, self.mixer)]
+        if self.feed_forward is not None:
+            out += [(s.feed_forward_norm_name, self.feed_forward_norm), (s.feed_forward.weight_prefix, self.feed_forward)]
+        return out
+
+    def parts(self):
+        """The parts that may offer a prelude, a graph variant or weights to count."""
+        return [p for p in (self.mixer, self.feed_forward) if p is not None]
 
     def parameters(self) -> Dict[str, ParamSpec]:
         out = {}
         for prefix, part in self._children():
             for name, p in part.parameters().items():
-                out[f"{prefix}.{name}"] = p
+                out[f"{prefix}.{name}" if name else prefix] = p      # '' : the tensor is named like the part
         return out
 
     def load(self, tensors: Dict[str, torch.Tensor]) -> None:
         for prefix, part in self._children():
-            part.load({n[len(prefix) + 1:]: t for n, t in tensors.items() if n.startswith(prefix + ".")})
+            mine = {n[len(prefix) + 1:]: t for n, t in tensors.items() if n.startswith(prefix + ".")}
+            if prefix in tensors and "" in part.parameters():
+                mine[""] = tensors[prefix]
+            part.load({n: t for n, t in mine.items() if n in part.parameters()})
 
     def forward(self, h: torch.Tensor, delta: Optional[torch.Tensor], ctx: StageContext
                 ) -> Tuple[torch.Tensor, Optional[torch.Tensor]]:
@@ -70,3 +83,39 @@ def pre_norm(block: Block, h: torch.Tensor, delta: Optional[torch.Tensor], ctx: 
         extra["residual"] = h
     f = block.feed_forward.forward(y, **extra)
     return h, f
+
+
+@register_arrangement("branch_norm")
+def branch_norm(block: Block, h: torch.Tensor, delta: Optional[torch.Tensor], ctx: StageContext):
+    """h += norm1(mixer(h)); h += norm2(ffn(h)): the norms sit on the sublayers' outputs and the
+    sublayers read the stream itself.
+
+    `h` is the float32 residual stream and is complete on entry and on return (nothing is pending, so
+    `delta` passes through as None).  A sublayer's products want their input in the compute dtype: the
+    kernel that adds a normed output to the stream also writes the new stream in that dtype, and hands
+    it to the next sublayer, across layers too, through `batch.tables["stream_copy"]` (a pair of the
+    stream it is a copy of and the copy); the first layer of a model finds there what the embedding
+    kernel wrote.  In the float32 mode the stream is its own copy.
+    """
+    from ..csrc import ops
+    if delta is not None:
+        ops.residual_add(h, ops.as_tensor(delta))
+    tables = ctx.batch.tables
+    narrow = None if block.dtype == torch.float32 else block.dtype
+    held = tables.pop("stream_copy", None)
+    if narrow is None:
+        x = h
+    elif held is not None and held[0] is h:
+        x = held[1]
+    else:
+        x = h.to(narrow)
+    ctx.partials_ok = False
+    ctx.residual = None                                         # the norm stands between the product and the stream
+    a = block.mixer.forward(x, ctx)
+    x = block.mixer_norm.add_normed(h, a, narrow)
+    if block.feed_forward is not None:
+        f = block.feed_forward.forward(x if narrow is not None else h)
+        x = block.feed_forward_norm.add_normed(h, f, narrow)
+    if narrow is not None:
+        tables["stream_copy"] = (h, x)
+    return h, None

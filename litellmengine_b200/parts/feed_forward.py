@@ -23,19 +23,22 @@ class SwiGLU:
         if spec.intermediate_size <= 0:
             raise ValueError("intermediate_size must be positive")
         self.hidden, self.inter, self.dtype = hidden_size, spec.intermediate_size, compute_dtype
+        names = dict(getattr(spec, "tensor_names", ()))
+        self._gate, self._up, self._down = (names.get("gate", "gate_proj.weight"), names.get("up", "up_proj.weight"),
+                                            names.get("down", "down_proj.weight"))
         self.w_gate_up: Optional[torch.Tensor] = None
         self.w_down: Optional[torch.Tensor] = None
 
     def parameters(self) -> Dict[str, ParamSpec]:
-        return {"gate_proj.weight": ParamSpec((self.inter, self.hidden)),
-                "up_proj.weight": ParamSpec((self.inter, self.hidden)),
-                "down_proj.weight": ParamSpec((self.hidden, self.inter))}
+        return {self._gate: ParamSpec((self.inter, self.hidden)),
+                self._up: ParamSpec((self.inter, self.hidden)),
+                self._down: ParamSpec((self.hidden, self.inter))}
 
     def load(self, t: Dict[str, torch.Tensor]) -> None:
-        g, u = t["gate_proj.weight"], t["up_proj.weight"]
+        g, u = t[self._gate], t[self._up]
         dt = torch.float32 if torch.float32 in (g.dtype, u.dtype) else g.dtype
         self.w_gate_up = torch.cat([g.to(dt), u.to(dt)], dim=0).contiguous()
-        self.w_down = t["down_proj.weight"].contiguous()
+        self.w_down = t[self._down].contiguous()
         ops.prepare_streaming(self.w_gate_up)       # a tiled copy for decode steps (bfloat16 on a GPU only)
         ops.prepare_streaming(self.w_down)
 

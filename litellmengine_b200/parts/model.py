@@ -38,6 +38,11 @@ class Model:
         self.device = torch.device(device)
         self.blocks: List[Block] = [Block(b, plan.hidden_size, self.dtype, self.device) for b in plan.blocks]
         self.final_norm = lookup("norm", plan.final_norm.kind)(plan.final_norm, plan.hidden_size)
+        # an encoding that is added to the embeddings themselves (a mixer's own encoding is the mixer's)
+        self.embedding_position = None
+        if plan.embedding_position is not None:
+            self.embedding_position = lookup("position", plan.embedding_position.kind)(
+                plan.embedding_position, plan.hidden_size, self.device)
         self.embedding: Optional[torch.Tensor] = None
         self.output: Optional[torch.Tensor] = None
 
@@ -48,7 +53,7 @@ class Model:
         for spec, block in zip(p.blocks, self.blocks):
             for name, ps in block.parameters().items():
                 out[f"{spec.weight_prefix}.{name}"] = ps
-        out[p.final_norm_name] = self.final_norm.parameters()["weight"]
+        out[p.final_norm_name] = next(iter(self.final_norm.parameters().values()))
         out[p.output_name] = ParamSpec((p.vocab_size, p.hidden_size),
                                        optional_alias=p.embedding_name if p.tie_word_embeddings else None)
         return out
@@ -66,7 +71,7 @@ class Model:
         self.embedding = get(p.embedding_name).contiguous()
         for spec, block in zip(p.blocks, self.blocks):
             block.load({n: get(f"{spec.weight_prefix}.{n}") for n in block.parameters()})
-        self.final_norm.load({"weight": get(p.final_norm_name)})
+        self.final_norm.load({next(iter(self.final_norm.parameters())): get(p.final_norm_name)})
         self.output = self.embedding if p.output_name in aliased else get(p.output_name).contiguous()
         ops.prepare_streaming(self.output)          # a tiled copy of the output head for decode steps
 
@@ -84,10 +89,11 @@ class Model:
         `step_prelude()` method)."""
         out = []
         for b in self.blocks:
-            for part in (b.mixer, b.feed_forward):
+            for part in b.parts():
                 make = getattr(part, "step_prelude", None)
-                if make is not None:
-                    out.append(make())
+                made = make() if make is not None else None
+                if made is not None:                              # one prelude, or several (a mixer made of mixers)
+                    out += list(made) if isinstance(made, (list, tuple)) else [made]
         return out
 
     def graph_variant(self, batch, padded: bool) -> tuple:
@@ -98,7 +104,7 @@ class Model:
         give the same `graph_variant_group` choose alike and are asked once."""
         out, seen = [], set()
         for b in self.blocks:
-            for part in (b.mixer, b.feed_forward):
+            for part in b.parts():
                 ask = getattr(part, "graph_variant", None)
                 group = getattr(part, "graph_variant_group", None)
                 if ask is None or (group is not None and group in seen):
@@ -118,7 +124,7 @@ class Model:
                 seen.add(t.data_ptr())
                 total += t.numel() * t.element_size()
         for b in self.blocks:
-            for part in (b.mixer, b.feed_forward):
+            for part in b.parts():
                 for v in vars(part).values():
                     if isinstance(v, torch.Tensor) and v.dim() == 2:
                         add(v)
@@ -130,7 +136,10 @@ class Model:
         """batch: StepBatch already on the device; cache: CacheManager.  Returns float32
         [batch.num_want, vocab] (an empty tensor when nothing is wanted)."""
         with ops.bound_stream():                       # one stream for the whole pass, looked up once
-            h = ops.embedding(batch.token_ids, self.embedding, batch.status, feedback=getattr(batch, "feedback", None))
+            if self.embedding_position is not None:
+                h = self.embedding_position.embed(batch, self.embedding, self.dtype)
+            else:
+                h = ops.embedding(batch.token_ids, self.embedding, batch.status, feedback=getattr(batch, "feedback", None))
             delta = None
             for s, st in enumerate(self.plan.order):
                 block = self.blocks[st.block]

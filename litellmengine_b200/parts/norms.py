@@ -21,13 +21,19 @@ class RMSNorm:
     def __init__(self, spec: NormSpec, size: int):
         self.eps = float(spec.eps)
         self.size = size
+        self.name = getattr(spec, "weight_name", "weight")     # '' when the tensor is named like the norm itself
         self.weight: Optional[torch.Tensor] = None
 
     def parameters(self) -> Dict[str, ParamSpec]:
-        return {"weight": ParamSpec((self.size,), role="scale", init=("one_plus_normal", 0.01))}
+        return {self.name: ParamSpec((self.size,), role="scale", init=("one_plus_normal", 0.01))}
 
     def load(self, tensors: Dict[str, torch.Tensor]) -> None:
-        self.weight = tensors["weight"].contiguous()
+        self.weight = tensors[self.name].contiguous()
+
+    def add_normed(self, h: torch.Tensor, y, copy_dtype: Optional[torch.dtype] = None) -> Optional[torch.Tensor]:
+        """h += norm(y) * weight in place (the norm of a sublayer's OUTPUT joined with the residual add);
+        returns the new h in `copy_dtype` if one is asked for."""
+        return ops.rmsnorm_add(h, y, self.weight, self.eps, copy_dtype)
 
     def forward(self, x: torch.Tensor, out_dtype: torch.dtype, delta: Optional[torch.Tensor] = None,
                 rows: Optional[torch.Tensor] = None, write_sum: bool = False) -> torch.Tensor:

@@ -39,6 +39,31 @@ class NoPosition:
         return None
 
 
+@register_position("sinusoid_added")
+class AddedSinusoid:
+    """A model's `embedding_position`: the vector with entry 2i = sin(p * theta^(-2i/width)) and entry
+    2i+1 = cos of the same angle is added to the embedding of the token at position p, in 32-bit, inside
+    the embedding kernel.  The frequencies are tabulated once in double precision, so that the angle is
+    exact to a float's last bit at any position.  `embed` returns the float32 stream; in a 16-bit run
+    mode the same rows in the compute dtype are left in `batch.tables["stream_copy"]` for a first layer
+    whose sublayers read the stream itself."""
+
+    def __init__(self, spec: PositionSpec, width: int, device):
+        if not spec.theta > 0:
+            raise ValueError("the sinusoid's base must be positive")
+        i = torch.arange((width + 1) // 2, dtype=torch.float64)
+        self.inv_freq = torch.pow(torch.tensor(float(spec.theta), dtype=torch.float64), -2.0 * i / width).to(device)
+
+    def embed(self, batch, table: torch.Tensor, compute_dtype: torch.dtype) -> torch.Tensor:
+        from ..csrc import ops
+        narrow = None if compute_dtype == torch.float32 else compute_dtype
+        h, copy = ops.embedding_sinusoid(batch.token_ids, table, batch.positions, self.inv_freq, batch.status,
+                                         feedback=getattr(batch, "feedback", None), copy_dtype=narrow)
+        if copy is not None and getattr(batch, "tables", None) is not None:
+            batch.tables["stream_copy"] = (h, copy)
+        return h
+
+
 @register_position("rope")
 class RotaryPosition:
     """Half-split rotation: inv_freq[i] = powf(theta, -(2 i) / rotary_dim) with theta and the

@@ -57,6 +57,8 @@ class ParamSpec:
     'index': an integer table; held as int32.
     init: ('normal', std) or ('one_plus_normal', std) for the random-weights mode.
     optional_alias: name of another tensor to use when this one is absent.
+    A dimension of -1 in `shape` is a size that only the stored tensor knows (the part reads it when it
+    is handed the tensor); the random-weights mode cannot draw such a tensor.
     """
     shape: Tuple[int, ...]
     role: str = "matrix"
@@ -180,6 +182,8 @@ class RandomSource(WeightSource):
         p = self._p[name]
         if p.role == "index":
             raise ValueError(f"{name}: no random rule for integer tables")
+        if any(d < 0 for d in p.shape):
+            raise ValueError(f"{name}: a size of this tensor is only known from stored weights; give it in the configuration")
         kind, std = p.init
         if kind not in ("normal", "one_plus_normal"):
             raise ValueError(f"{name}: unknown init {kind!r}")
@@ -215,7 +219,7 @@ def check_source(params: Dict[str, ParamSpec], source: WeightSource, where: str 
                 missing.append(name)
             continue
         found = tuple(source.shape(name))
-        if found != tuple(p.shape):
+        if len(found) != len(p.shape) or any(w != -1 and w != f for w, f in zip(p.shape, found)):
             wrong.append((name, tuple(p.shape), found))
     unexpected = sorted(have - set(params))
     if missing or unexpected or wrong:
