@@ -2,7 +2,7 @@
 """Benchmark of the engine on one B200.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--batch 8] [--layers L]
-                    [--impl ours|reference] [--points LIST | --no-points]
+                    [--impl ours|reference] [--points LIST | --no-points] [--design tobovik [--sizes LIST]]
 
 Headline (`value`): decode tokens/s of `batch` requests whose context ends at 4,096 tokens, on a
 model with the layer sizes of Qwen3-8B (36 layers unless --layers says fewer; the JSON names both
@@ -16,6 +16,11 @@ roofline, the same decode through the Python entry point (`e2e`: host ids in, ho
 `points`: decode at batch 1 and 64 with their roofline fractions, generation of 256 tokens after
 2,048-token prompts, the float32 path at batch 8, the Qwen3-0.6B shape with 32 mixed requests, and
 the Qwen3-32B shape at batch 16 (each sub-record names its sizes).
+
+`--design tobovik [--sizes w1024,w2048,w4096]` measures something else and prints a line of its own:
+prefill and decode of the Tobovik design beside Qwen3 at equal width, heads, feed-forward, depth and
+vocabulary, and the design's own kernels beside the like kernels of the Qwen3 path with their roofline
+fractions.  Without it the workload and the line above are what they always were.
 
 `--impl reference` times the unmodified reference engine (float32, its only precision) on the same
 shape, batch, context and steps through baseline/reference_arm.py and prints the same keys with
@@ -512,6 +517,200 @@ class Bench:
             points["qwen3_32b"] = {"skipped": "out of device memory: " + str(e)[:80]}
 
 
+# ---- another design beside its closest model ----------------------------------------------------------
+# `--design tobovik`: prefill and decode of the Tobovik design at a few sizes that resemble a real model's
+# layers (random weights), beside Qwen3 at equal width, heads, feed-forward, depth and vocabulary, and the
+# design's own kernels one by one beside the like kernels of the Qwen3 path with their roofline
+# fractions.  The default workload and its JSON line do not change.
+DESIGN_VOCAB = 32768
+DESIGN_SIZES = {            # width, feed-forward, query heads, kv heads, layers
+    "w1024": (1024, 3072, 8, 4, 8),
+    "w2048": (2048, 6144, 16, 8, 8),
+    "w4096": (4096, 12288, 32, 8, 4),
+}
+DESIGN_HEAD = 128
+
+
+def tobovik_dict(width, ff, heads, kv, layers):
+    """Three parallel layers, then a gla layer, and so on; key and value heads of 128 so that the softmax side
+    takes the same tuned attention kernels as Qwen3; the linear-attention side a quarter of the heads."""
+    mlp = {"kind": "dense", "ff": ff}
+    par = {"type": "parallel", "mlp": mlp, "mixer": {
+        "left": {"heads": heads, "kv_heads": kv, "dim": DESIGN_HEAD, "vdim": DESIGN_HEAD, "scale": DESIGN_HEAD ** -0.5,
+                 "q_temp": {"coef": 0.3, "every": 128}},
+        "right": {"heads": max(1, heads // 4), "dim": DESIGN_HEAD, "vdim": DESIGN_HEAD, "tau": 16.0, "rank": 64},
+        "left_scale": 0.8, "right_scale": 0.9}}
+    gla = {"type": "gla", "mlp": mlp,
+           "mixer": {"heads": max(1, heads // 2), "dim": DESIGN_HEAD, "vdim": DESIGN_HEAD, "tau": 16.0, "rank": 64}}
+    return {"architecture": "Tobovik", "vocab": DESIGN_VOCAB, "width": width, "norm": {"eps": 1e-5},
+            "layers": [gla if i % 4 == 3 else par for i in range(layers)]}
+
+
+def design_bench(args, pk) -> int:
+    import torch
+    from litellmengine_b200.config import config_from_dict
+    from litellmengine_b200.csrc import ops
+    from litellmengine_b200.csrc.microbench import Flusher, timed
+    from litellmengine_b200.engine import ModelRunner, StepEntry
+    torch.cuda.set_device(0)
+    dev = "cuda:0"
+    gen = torch.Generator().manual_seed(3)
+    toks = lambda n: torch.randint(0, DESIGN_VOCAB, (n,), generator=gen).tolist()
+    prompt_len, context, batches = 2048, 1024, (8, 32)
+    ev = lambda: torch.cuda.Event(enable_timing=True)
+
+    def measure(config):
+        runner = ModelRunner.from_config(config, seed=1, dtype="bfloat16", device=dev, page_size=PAGE,
+                                         max_total_tokens=max(batches) * (context + 64) + prompt_len, max_requests=max(batches),
+                                         max_tokens_per_step=prompt_len)
+        rec, times = {}, []
+        for i in range(args.warmup + 3):                       # one prompt in one step
+            s = runner.admit()
+            a, b = ev(), ev()
+            a.record()
+            runner.step([StepEntry(s, toks(prompt_len), [prompt_len - 1])])
+            b.record()
+            torch.cuda.synchronize()
+            runner.release(s)
+            if i >= args.warmup:
+                times.append(a.elapsed_time(b))
+        rec["prefill_2048_ms"] = round(sum(times) / len(times), 3)
+        rec["prefill_2048_tok_s"] = round(prompt_len / (rec["prefill_2048_ms"] * 1e-3), 1)
+        for B in batches:
+            steps = args.steps
+            slots = [runner.admit() for _ in range(B)]
+            for s in slots:
+                runner.step([StepEntry(s, toks(context - steps - args.warmup), [])])
+            feed = [toks(B) for _ in range(steps + args.warmup)]
+            torch.cuda.synchronize()
+            for i in range(args.warmup):
+                runner.step([StepEntry(s, [feed[i][j]], [0]) for j, s in enumerate(slots)])
+            torch.cuda.synchronize()
+            n0 = ops.launch_count
+            a, b = ev(), ev()
+            a.record()
+            for i in range(args.warmup, args.warmup + steps):
+                runner.step([StepEntry(s, [feed[i][j]], [0]) for j, s in enumerate(slots)])
+            b.record()
+            torch.cuda.synchronize()
+            ms = a.elapsed_time(b) / steps
+            state = sum(t[0].numel() * t.element_size() for k, t in runner.cache.state.items() if isinstance(k, int))
+            step_bytes = runner.model.weight_bytes() + B * (runner.cache.bytes_per_token() * (context - steps // 2) + 2 * state)
+            rec[f"decode_b{B}_ms"] = round(ms, 4)
+            rec[f"decode_b{B}_tok_s"] = round(B / (ms * 1e-3), 1)
+            rec[f"decode_b{B}_hbm_frac"] = round(step_bytes / (ms * 1e-3) / 1e9 / pk["hbm_gbs"], 4)
+            rec[f"decode_b{B}_launches_per_step"] = (ops.launch_count - n0) // steps
+            for s in slots:
+                runner.release(s)
+        runner.check_status()
+        return rec
+
+    sizes = {}
+    for name, (width, ff, heads, kv, layers) in DESIGN_SIZES.items():
+        if args.sizes and name not in args.sizes.split(","):
+            continue
+        qwen = dict(QWEN3_8B, num_hidden_layers=layers, hidden_size=width, num_attention_heads=heads, num_key_value_heads=kv,
+                    head_dim=DESIGN_HEAD, intermediate_size=ff, vocab_size=DESIGN_VOCAB)
+        sizes[name] = {"shape": {"width": width, "ff": ff, "heads": heads, "kv_heads": kv, "layers": layers, "vocab": DESIGN_VOCAB}}
+        for label, cfg in (("tobovik", tobovik_dict(width, ff, heads, kv, layers)), ("qwen3", qwen)):
+            sizes[name][label] = measure(config_from_dict(cfg))
+            gc.collect()
+            torch.cuda.empty_cache()
+        t, q = sizes[name]["tobovik"], sizes[name]["qwen3"]
+        sizes[name]["tobovik_over_qwen3"] = {k: round(t[k] / q[k], 3) for k in t if k.endswith("tok_s")}
+
+    # the design's own kernels beside the like kernels of the Qwen3 path, at the largest size's widths
+    flush = Flusher(dev)
+    width, _, heads, kv, _ = DESIGN_SIZES["w4096"]
+    T, hbm = prompt_len, pk["hbm_gbs"] * 1e9
+    kernels = {}
+
+    def add(name, fn, nbytes=None, flops=None, peak_flops=None):
+        sec = timed(fn, 5, 3, flush)
+        rec = {"us": round(sec * 1e6, 2)}
+        if nbytes is not None:
+            rec.update(gbs=round(nbytes / sec / 1e9, 1), frac_of_hbm=round(nbytes / sec / hbm, 4))
+        if flops is not None:
+            rec.update(tflops=round(flops / sec / 1e12, 2), frac_of_fp32_peak=round(flops / sec / peak_flops, 4))
+        kernels[name] = rec
+
+    h = torch.randn(T, width, device=dev)
+    y = torch.randn(T, width, device=dev)
+    w = torch.ones(width, device=dev)
+    add("rmsnorm_add (new: norm of a branch output + residual add + copy)", lambda: ops.rmsnorm_add(h, y, w, 1e-5, torch.bfloat16),
+        nbytes=T * width * (4 + 4 + 4 + 2))
+    add("rmsnorm (like: residual add + norm)", lambda: ops.rmsnorm(h, w, 1e-5, torch.bfloat16, delta=y, write_sum=True),
+        nbytes=T * width * (4 + 4 + 4 + 2))
+    ids = torch.randint(0, DESIGN_VOCAB, (T,), device=dev, dtype=torch.int32)
+    table = torch.randn(DESIGN_VOCAB, width, device=dev).to(torch.bfloat16)
+    pos = torch.arange(T, device=dev, dtype=torch.int32)
+    status = torch.zeros(2, dtype=torch.int32, device=dev)
+    inv = torch.pow(torch.tensor(10000.0, dtype=torch.float64), -2.0 * torch.arange(width // 2, dtype=torch.float64) / width).to(dev)
+    add("embedding_sinusoid (new)", lambda: ops.embedding_sinusoid(ids, table, pos, inv, status, copy_dtype=torch.bfloat16),
+        nbytes=T * width * (2 + 4 + 2))
+    add("embedding (like)", lambda: ops.embedding(ids, table, status), nbytes=T * width * (2 + 4))
+    d = DESIGN_HEAD
+    pages = T // PAGE
+    proj = torch.randn(T, (heads + 2 * kv) * d + heads * d, device=dev)
+    cache = torch.zeros(pages, 2, kv, PAGE, d, device=dev, dtype=torch.bfloat16)
+    tbl = torch.arange(pages, device=dev, dtype=torch.int32).view(1, pages)
+    ent, slot0 = torch.zeros(T, device=dev, dtype=torch.int32), torch.zeros(1, device=dev, dtype=torch.int32)
+    bq, bk, bv = (torch.zeros(n * d, device=dev) for n in (heads, kv, kv))
+    qw, kw = torch.ones(heads * d, device=dev), torch.ones(kv * d, device=dev)
+    prep_bytes = T * ((heads + 2 * kv) * d * 4 + (heads + 2 * kv) * d * 2)
+    add("attention_prepare (new: bias, projection norm, temperature, page write)",
+        lambda: ops.attention_prepare(proj, 0, heads * d, (heads + kv) * d, (bq, bk, bv), qw, kw, "projection", 1e-5, (0.3, 128),
+                                      cache[:, 0], cache[:, 1], pos, ent, slot0, tbl, heads, kv, d, d, PAGE, status, torch.bfloat16),
+        nbytes=prep_bytes)
+    qkv = proj[:, :(heads + 2 * kv) * d].contiguous()
+    hw = torch.ones(d, device=dev)
+    invf = torch.pow(torch.tensor(1e6), -torch.arange(0, d, 2, dtype=torch.float32) / d).to(dev)
+    add("qk_norm_rope_kv_write (like: head norm, rotation, page write)",
+        lambda: ops.qk_norm_rope_kv_write(qkv, cache, pos, ent, slot0, tbl, hw, hw, 1e-6, invf, d, heads, kv, d, PAGE, True, status,
+                                          q_dtype=torch.bfloat16), nbytes=prep_bytes)
+    a_out = torch.randn(T, heads * d, device=dev).to(torch.bfloat16)
+    gate = torch.randn(T, heads * d, device=dev)
+    out = torch.empty(T, heads * d, device=dev, dtype=torch.bfloat16)
+    add("gate_mul (new: output gate)", lambda: ops.gate_mul(a_out, gate, 0, out, 0, "sigmoid", 0.8), nbytes=T * heads * d * (2 + 4 + 2))
+    gu = torch.randn(T, 2 * heads * d, device=dev).to(torch.bfloat16)
+    add("silu_and_mul (like)", lambda: ops.silu_and_mul(gu), nbytes=T * heads * d * (2 + 2 + 2))
+    # the recurrence: prompt portion (chunks side by side) and single decoded tokens
+    H, D, V = heads // 4, d, d
+    gp = torch.randn(T, 2 * H * D + 2 * H * V, device=dev)
+    la = -torch.rand(T, H * D, device=dev) * 0.1
+    nw = torch.ones(V, device=dev)
+    offs = (0, H * D, 2 * H * D, 2 * H * D + H * V)
+    gout = torch.empty(T, H * V, device=dev, dtype=torch.bfloat16)
+    B = 64
+    state = torch.zeros(B, H, D, V, device=dev)
+    items = torch.tensor([(0, c, 64, i) for i, c in enumerate(range(0, T, 64))], device=dev, dtype=torch.int32)
+    chains = torch.tensor([(0, 0, T // 64)], device=dev, dtype=torch.int32)
+    ss, sa = torch.empty(T // 64, H, D, V, device=dev), torch.empty(T // 64, H, D, device=dev)
+    q0, qn = torch.zeros(1, device=dev, dtype=torch.int32), torch.full((1,), T, device=dev, dtype=torch.int32)
+    args_c = (gp, offs, la, nw, 1e-5, D ** -0.5, 0.9, gout, 0, state, slot0, q0, qn)
+
+    def chunked():
+        ops.gla_scan(*args_c, items, T // 64, ops.GLA_LOCAL, ss, sa, H, D, V)
+        ops.gla_chain(state, ss, sa, chains, 1, slot0, H, D, V)
+        ops.gla_scan(*args_c, items, T // 64, ops.GLA_OUT, ss, sa, H, D, V)
+    props = torch.cuda.get_device_properties(0)
+    fp32_peak = props.multi_processor_count * 128 * 2 * 1.965e9
+    add("gla_scan, one 2048-token portion in chunks of 64 (new; 32-bit recurrence on CUDA cores)", chunked,
+        flops=T * H * D * V * (2 + 2 + 2), peak_flops=fp32_peak)
+    slots = torch.arange(B, device=dev, dtype=torch.int32)
+    dq0, dqn = torch.arange(B, device=dev, dtype=torch.int32), torch.ones(B, device=dev, dtype=torch.int32)
+    args_d = (gp[:B], offs, la[:B], nw, 1e-5, D ** -0.5, 0.9, gout[:B], 0, state, slots, dq0, dqn)
+    add(f"gla_scan, {B} single tokens (new; reads and writes each state once)",
+        lambda: ops.gla_scan(*args_d, None, B, ops.GLA_FULL, None, None, H, D, V), nbytes=2 * B * H * D * V * 4)
+    print(json.dumps({"metric": "tokens/s of the Tobovik design beside Qwen3 at equal sizes (bfloat16, random weights)",
+                      "design": "tobovik", "prompt_tokens": prompt_len, "decode_context": context, "steps": args.steps,
+                      "warmup": args.warmup, "sizes": sizes, "kernels_at_w4096": kernels,
+                      "peaks": {"hbm_gbs": pk["hbm_gbs"], "fp32_fma_tflops_nominal": round(fp32_peak / 1e12, 1),
+                                "source": pk["source"]},
+                      "l2": "kernel timings: a 256 MB buffer is overwritten between launches; steps read every weight"}))
+    return 0
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -523,6 +722,9 @@ def main() -> int:
     ap.add_argument("--points", default=",".join(ALL_POINTS),
                     help="which extra measurements to take: " + ",".join(ALL_POINTS))
     ap.add_argument("--no-points", action="store_true", help="the headline, prefill and e2e only")
+    ap.add_argument("--design", choices=["tobovik"],
+                    help="instead of the default workload: this design beside Qwen3 at equal sizes, and its kernels")
+    ap.add_argument("--sizes", default="", help="with --design: which of " + ",".join(DESIGN_SIZES) + " (default: all)")
     args = ap.parse_args()
 
     if args.gpus != 1:
@@ -538,6 +740,8 @@ def main() -> int:
         ap.error(f"unknown points {sorted(unknown)}; choose from {ALL_POINTS}")
 
     pk = peaks()
+    if args.design:
+        return design_bench(args, pk)
     bench = Bench(args, pk)
     points = {}
     main_rec = bench.qwen3_8b(want_points, points)

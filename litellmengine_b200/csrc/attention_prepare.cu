@@ -17,6 +17,20 @@
 
 #define AP_THREADS 256
 
+__device__ __forceinline__ float4 ld4(const float* p) { return *reinterpret_cast<const float4*>(p); }
+__device__ __forceinline__ void st4(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
+__device__ __forceinline__ void st4(bf16* p, float4 v) {
+    uint2 raw;
+    __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&raw);
+    h[0] = __floats2bfloat162_rn(v.x, v.y);
+    h[1] = __floats2bfloat162_rn(v.z, v.w);
+    *reinterpret_cast<uint2*>(p) = raw;
+}
+__device__ __forceinline__ float4 add4(float4 a, float4 b) { return make_float4(a.x + b.x, a.y + b.y, a.z + b.z, a.w + b.w); }
+__device__ __forceinline__ float4 mul4(float4 a, float4 b) { return make_float4(a.x * b.x, a.y * b.y, a.z * b.z, a.w * b.w); }
+__device__ __forceinline__ float4 scale4(float4 a, float s) { return make_float4(a.x * s, a.y * s, a.z * s, a.w * s); }
+__device__ __forceinline__ float sq4(float4 a) { return a.x * a.x + a.y * a.y + a.z * a.z + a.w * a.w; }
+
 template <typename TQ, typename TC>
 __global__ void attention_prepare_kernel(
     const float* __restrict__ proj, long long proj_stride, int q_off, int k_off, int v_off,
@@ -27,7 +41,7 @@ __global__ void attention_prepare_kernel(
     long long key_page_stride, long long value_page_stride,
     const int32_t* __restrict__ positions, const int32_t* __restrict__ token_entry,
     const int32_t* __restrict__ entry_slot, const int32_t* __restrict__ block_table, int table_stride,
-    int nq, int nkv, int dk, int dv, int page_size, int num_pages, int32_t* __restrict__ status) {
+    int nq, int nkv, int dk, int dv, int page_size, int num_pages, int vec, int32_t* __restrict__ status) {
     pdl_begin();
     extern __shared__ __align__(16) float smem[];
     const int nqe = nq * dk, nke = nkv * dk, nve = nkv * dv;
@@ -39,25 +53,50 @@ __global__ void attention_prepare_kernel(
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
 
     float ssq = 0.0f, ssk = 0.0f;
-    for (int i = threadIdx.x; i < nqe; i += blockDim.x) {
-        const float a = row[q_off + i] + (bq ? bq[i] : 0.0f);
-        fq[i] = a;
-        ssq += a * a;
-    }
-    if (keys)
-        for (int i = threadIdx.x; i < nke; i += blockDim.x) {
-            const float a = row[k_off + i] + (bk ? bk[i] : 0.0f);
-            fk[i] = a;
-            ssk += a * a;
+    if (vec) {                                  // every width and offset a multiple of four floats: 16-byte accesses
+        for (int i = threadIdx.x * 4; i < nqe; i += blockDim.x * 4) {
+            float4 a = ld4(row + q_off + i);
+            if (bq) a = add4(a, ld4(bq + i));
+            st4(fq + i, a);
+            ssq += sq4(a);
         }
+        if (keys)
+            for (int i = threadIdx.x * 4; i < nke; i += blockDim.x * 4) {
+                float4 a = ld4(row + k_off + i);
+                if (bk) a = add4(a, ld4(bk + i));
+                st4(fk + i, a);
+                ssk += sq4(a);
+            }
+    } else {
+        for (int i = threadIdx.x; i < nqe; i += blockDim.x) {
+            const float a = row[q_off + i] + (bq ? bq[i] : 0.0f);
+            fq[i] = a;
+            ssq += a * a;
+        }
+        if (keys)
+            for (int i = threadIdx.x; i < nke; i += blockDim.x) {
+                const float a = row[k_off + i] + (bk ? bk[i] : 0.0f);
+                fk[i] = a;
+                ssk += a * a;
+            }
+    }
     if (norm_scope == 2) {
+        // each thread scales what it wrote itself, so no barrier stands between the two passes but the sums'
         const float tq = block_sum(ssq, scratch);
         const float iq = 1.0f / sqrtf(tq / static_cast<float>(nqe) + eps);
-        for (int i = threadIdx.x; i < nqe; i += blockDim.x) fq[i] = fq[i] * iq * (qw ? qw[i] : 1.0f);
+        if (vec)
+            for (int i = threadIdx.x * 4; i < nqe; i += blockDim.x * 4)
+                st4(fq + i, qw ? mul4(scale4(ld4(fq + i), iq), ld4(qw + i)) : scale4(ld4(fq + i), iq));
+        else
+            for (int i = threadIdx.x; i < nqe; i += blockDim.x) fq[i] = fq[i] * iq * (qw ? qw[i] : 1.0f);
         if (keys) {
             const float tk = block_sum(ssk, scratch);
             const float ik = 1.0f / sqrtf(tk / static_cast<float>(nke) + eps);
-            for (int i = threadIdx.x; i < nke; i += blockDim.x) fk[i] = fk[i] * ik * (kw ? kw[i] : 1.0f);
+            if (vec)
+                for (int i = threadIdx.x * 4; i < nke; i += blockDim.x * 4)
+                    st4(fk + i, kw ? mul4(scale4(ld4(fk + i), ik), ld4(kw + i)) : scale4(ld4(fk + i), ik));
+            else
+                for (int i = threadIdx.x; i < nke; i += blockDim.x) fk[i] = fk[i] * ik * (kw ? kw[i] : 1.0f);
         }
     } else if (norm_scope == 1) {
         __syncthreads();
@@ -77,7 +116,10 @@ __global__ void attention_prepare_kernel(
     float temp = 1.0f;
     if (temp_every > 0) temp = 1.0f + temp_coef * logf(static_cast<float>((pos + 1) / temp_every + 1));
     TQ* qo = q_out + static_cast<size_t>(t) * nqe;
-    for (int i = threadIdx.x; i < nqe; i += blockDim.x) qo[i] = from_f32<TQ>(fq[i] * temp);
+    if (vec)
+        for (int i = threadIdx.x * 4; i < nqe; i += blockDim.x * 4) st4(qo + i, scale4(ld4(fq + i), temp));
+    else
+        for (int i = threadIdx.x; i < nqe; i += blockDim.x) qo[i] = from_f32<TQ>(fq[i] * temp);
     if (!keys) return;
 
     const int slot = entry_slot[token_entry[t]];
@@ -90,6 +132,19 @@ __global__ void attention_prepare_kernel(
     const int in_page = pos % page_size;
     TC* kp = keys + static_cast<size_t>(page) * key_page_stride;
     TC* vp = values + static_cast<size_t>(page) * value_page_stride;
+    if (vec) {
+        for (int i = threadIdx.x * 4; i < nke; i += blockDim.x * 4) {
+            const int head = i / dk, e = i - head * dk;
+            st4(kp + (static_cast<size_t>(head) * page_size + in_page) * dk + e, ld4(fk + i));
+        }
+        for (int i = threadIdx.x * 4; i < nve; i += blockDim.x * 4) {
+            const int head = i / dv, e = i - head * dv;
+            float4 a = ld4(row + v_off + i);
+            if (bv) a = add4(a, ld4(bv + i));
+            st4(vp + (static_cast<size_t>(head) * page_size + in_page) * dv + e, a);
+        }
+        return;
+    }
     for (int i = threadIdx.x; i < nke; i += blockDim.x) {
         const int head = i / dk, e = i - head * dk;
         kp[(static_cast<size_t>(head) * page_size + in_page) * dk + e] = from_f32<TC>(fk[i]);
@@ -116,6 +171,11 @@ extern "C" int llm_attention_prepare(
     if (smem > 200 * 1024) return LLM_REFUSED_SIZE;
     cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
     if (!keys) cache_dtype = q_dtype;
+    const bool fours = dk % 4 == 0 && dv % 4 == 0 && proj_stride % 4 == 0 && q_off % 4 == 0 && k_off % 4 == 0 &&
+                       v_off % 4 == 0 && key_page_stride % 4 == 0 && value_page_stride % 4 == 0;
+    const int vec = fours && aligned16(proj) && aligned16(q_out) && (!keys || (aligned16(keys) && aligned16(values))) &&
+                    (!bq || aligned16(bq)) && (!bk || aligned16(bk)) && (!bv || aligned16(bv)) &&
+                    (!qw || aligned16(qw)) && (!kw || aligned16(kw));
 #define LAUNCH(TQ, TC)                                                                                            \
     do {                                                                                                          \
         auto kern = attention_prepare_kernel<TQ, TC>;                                                             \
@@ -128,7 +188,7 @@ extern "C" int llm_attention_prepare(
                    bk, bv, qw, kw, norm_scope, eps, temp_coef, temp_every, static_cast<TQ*>(q_out),               \
                    static_cast<TC*>(keys), static_cast<TC*>(values), key_page_stride, value_page_stride,          \
                    positions, token_entry, entry_slot, block_table, table_stride, nq, nkv, dk, dv, page_size,     \
-                   num_pages, status);                                                                            \
+                   num_pages, vec, status);                                                                       \
     } while (0)
     if (q_dtype == LLM_DT_F32 && cache_dtype == LLM_DT_F32) LAUNCH(float, float);
     else if (q_dtype == LLM_DT_BF16 && cache_dtype == LLM_DT_BF16) LAUNCH(bf16, bf16);
@@ -146,9 +206,27 @@ extern "C" int llm_attention_prepare(
 template <typename T>
 __global__ void gate_mul_kernel(const T* __restrict__ a, const float* __restrict__ g, long long g_stride, int g_off,
                                 T* __restrict__ out, long long out_stride, int out_off, int width, int gate_kind,
-                                float scale) {
+                                float scale, int vec) {
     pdl_begin();
     const size_t t = blockIdx.y;
+    if (vec) {                                       // 16-byte accesses, 8 elements a thread a trip
+        for (int i = (blockIdx.x * blockDim.x + threadIdx.x) * 8; i < width; i += gridDim.x * blockDim.x * 8) {
+            float x[8], z[8];
+            load8(a + t * width + i, x);
+            if (gate_kind != 0) {
+                load8(g + t * g_stride + g_off + i, z);
+#pragma unroll
+                for (int u = 0; u < 8; ++u) {
+                    const float s = 1.0f / (1.0f + expf(-z[u]));
+                    x[u] *= (gate_kind == 2 ? z[u] * s : s);
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < 8; ++u) x[u] *= scale;
+            store8(out + t * out_stride + out_off + i, x);
+        }
+        return;
+    }
     for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < width; i += gridDim.x * blockDim.x) {
         float gate = 1.0f;
         if (gate_kind != 0) {
@@ -166,15 +244,19 @@ extern "C" int llm_gate_mul(const void* a, int dtype, const float* g, long long 
     if (num_tokens <= 0) return LLM_OK;
     if (width <= 0 || num_tokens > 65535 || gate_kind < 0 || gate_kind > 2 || (gate_kind && !g)) return LLM_REFUSED_SIZE;
     const int threads = 256;
-    const int bx = (width + threads - 1) / threads;
+    const int esz = dtype == LLM_DT_F32 ? 4 : 2;
+    const int vec = width % 8 == 0 && out_stride % 8 == 0 && out_off % 8 == 0 && aligned16(a) && aligned16(out) &&
+                    (!g || (aligned16(g) && g_stride % 4 == 0 && g_off % 4 == 0)) && esz > 0;
+    const int per_row = vec ? width / 8 : width;
+    const int bx = (per_row + threads - 1) / threads;
     const dim3 grid(bx < 64 ? bx : 64, num_tokens);
     cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
     if (dtype == LLM_DT_F32)
         launch_pdl((gate_mul_kernel<float>), grid, dim3(threads), 0, s, static_cast<const float*>(a), g, g_stride, g_off,
-                   static_cast<float*>(out), out_stride, out_off, width, gate_kind, scale);
+                   static_cast<float*>(out), out_stride, out_off, width, gate_kind, scale, vec);
     else if (dtype == LLM_DT_BF16)
         launch_pdl((gate_mul_kernel<bf16>), grid, dim3(threads), 0, s, static_cast<const bf16*>(a), g, g_stride, g_off,
-                   static_cast<bf16*>(out), out_stride, out_off, width, gate_kind, scale);
+                   static_cast<bf16*>(out), out_stride, out_off, width, gate_kind, scale, vec);
     else
         return LLM_REFUSED_DTYPE;
     return launch_status();

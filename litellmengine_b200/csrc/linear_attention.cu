@@ -12,10 +12,11 @@
 //                    input is never rounded.
 // gla_scan_kernel    one block per (work item, head) walks the item's tokens in order.  Thread (dg, v)
 //                    keeps rows dg*R .. dg*R+R-1 of column v of the state in registers; tokens are
-//                    staged through shared memory sixteen at a time; the partial sums of o over the row
-//                    groups meet in shared memory (one barrier a token).  Epilogue per staged batch, a
-//                    warp per token: RMS norm of o over V, weight, output gate silu(g), scale, store in
-//                    the compute dtype into a column range of the layer's output buffer.
+//                    staged through shared memory sixteen at a time (no barrier between the tokens of a
+//                    batch: each row group leaves its share of o in shared memory).  Epilogue per staged
+//                    batch, a warp per token: the row groups' shares are added, then RMS norm of o over V,
+//                    weight, output gate silu(g), scale, store in the compute dtype into a column range
+//                    of the layer's output buffer.
 //                    Three modes make long prompt portions parallel over chunks of tokens:
 //                      FULL   state in from the request's slot, outputs, state out to the slot
 //                             (single decoded tokens and short portions: one pass)
@@ -94,9 +95,11 @@ __global__ void gla_scan_kernel(
     float* sk = sq + GLA_TB * D;
     float* sa = sk + GLA_TB * D;
     float* sv = sa + GLA_TB * D;                    // [TB][V]
-    float* so = sv + GLA_TB * V;                    // [TB][V]
-    float* part = so + GLA_TB * V;                  // [2][DG][V]
+    float* part = sv + GLA_TB * V;                  // [TB][DG][V]: each row group's share of o, added up in the epilogue
     const size_t HD = static_cast<size_t>(H) * D;
+    const bool outputs = mode != GLA_LOCAL;
+    // a thread whose R rows all exist reads its decays, keys and queries sixteen bytes at a time
+    const bool whole = active && dg * R + R <= D && (D & 3) == 0;
 
     float S[R];
     float* slot_state = state + (static_cast<size_t>(entry_slot[entry]) * H + h) * D * V;
@@ -116,7 +119,7 @@ __global__ void gla_scan_kernel(
             const float* pr = proj + (base + tok) * stride + h * D + d;
             sk[idx] = pr[k_off];
             sa[idx] = expf(la[(base + tok) * HD + h * D + d]);
-            if (mode != GLA_LOCAL) sq[idx] = pr[q_off] * q_scale;
+            if (outputs) sq[idx] = pr[q_off] * q_scale;
         }
         for (int idx = tid; idx < nb * V; idx += nthreads) {
             const int tok = idx / V, c = idx - tok * V;
@@ -129,36 +132,56 @@ __global__ void gla_scan_kernel(
             const float* k = sk + tok * D + dg * R;
             const float* q = sq + tok * D + dg * R;
             float p0 = 0.0f, p1 = 0.0f;
-            if (mode == GLA_LOCAL) {
+            if (whole) {
+                const float4* a4 = reinterpret_cast<const float4*>(a);
+                const float4* k4 = reinterpret_cast<const float4*>(k);
+                const float4* q4 = reinterpret_cast<const float4*>(q);
+                if (outputs) {
 #pragma unroll
-                for (int r = 0; r < R; ++r)
-                    if (active && dg * R + r < D) S[r] = a[r] * S[r] + k[r] * vt;
-            } else {
+                    for (int r = 0; r < R; r += 4) {
+                        const float4 av = a4[r >> 2], kv = k4[r >> 2], qv = q4[r >> 2];
+                        S[r] = av.x * S[r] + kv.x * vt;             p0 += S[r] * qv.x;
+                        S[r + 1] = av.y * S[r + 1] + kv.y * vt;     p1 += S[r + 1] * qv.y;
+                        S[r + 2] = av.z * S[r + 2] + kv.z * vt;     p0 += S[r + 2] * qv.z;
+                        S[r + 3] = av.w * S[r + 3] + kv.w * vt;     p1 += S[r + 3] * qv.w;
+                    }
+                } else {
+#pragma unroll
+                    for (int r = 0; r < R; r += 4) {
+                        const float4 av = a4[r >> 2], kv = k4[r >> 2];
+                        S[r] = av.x * S[r] + kv.x * vt;
+                        S[r + 1] = av.y * S[r + 1] + kv.y * vt;
+                        S[r + 2] = av.z * S[r + 2] + kv.z * vt;
+                        S[r + 3] = av.w * S[r + 3] + kv.w * vt;
+                    }
+                }
+            } else if (active) {
 #pragma unroll
                 for (int r = 0; r < R; r += 2) {
-                    if (active && dg * R + r < D) { S[r] = a[r] * S[r] + k[r] * vt; p0 += S[r] * q[r]; }
-                    if (active && dg * R + r + 1 < D) { S[r + 1] = a[r + 1] * S[r + 1] + k[r + 1] * vt; p1 += S[r + 1] * q[r + 1]; }
-                }
-                if (DG == 1) {
-                    if (active) so[tok * V + v] = p0 + p1;
-                } else {
-                    float* pp = part + (tok & 1) * DG * V;
-                    if (active) pp[dg * V + v] = p0 + p1;
-                    __syncthreads();
-                    if (active && dg == 0) {
-                        float o = 0.0f;
-                        for (int g2 = 0; g2 < DG; ++g2) o += pp[g2 * V + v];
-                        so[tok * V + v] = o;
+                    if (dg * R + r < D) {
+                        S[r] = a[r] * S[r] + k[r] * vt;
+                        if (outputs) p0 += S[r] * q[r];
+                    }
+                    if (dg * R + r + 1 < D) {
+                        S[r + 1] = a[r + 1] * S[r + 1] + k[r + 1] * vt;
+                        if (outputs) p1 += S[r + 1] * q[r + 1];
                     }
                 }
             }
+            if (outputs && active) part[(tok * DG + dg) * V + v] = p0 + p1;
         }
         __syncthreads();
-        if (mode != GLA_LOCAL) {                    // a warp per token: norm over V, weight, gate, scale
+        if (outputs) {                              // a warp per token: add the row groups, norm over V, weight, gate, scale
             const int warp = tid >> 5, lane = tid & 31, nwarps = nthreads >> 5;
             for (int tok = warp; tok < nb; tok += nwarps) {
+                float* o = part + tok * DG * V;
                 float ss = 0.0f;
-                for (int c = lane; c < V; c += 32) ss += so[tok * V + c] * so[tok * V + c];
+                for (int c = lane; c < V; c += 32) {
+                    float sum = o[c];
+                    for (int g2 = 1; g2 < DG; ++g2) sum += o[g2 * V + c];
+                    o[c] = sum;
+                    ss += sum * sum;
+                }
                 ss = warp_sum(ss);
                 const float inv = 1.0f / sqrtf(ss / static_cast<float>(V) + eps);
                 const float* gr = proj + (base + tok) * stride + g_off + h * V;
@@ -166,7 +189,7 @@ __global__ void gla_scan_kernel(
                 for (int c = lane; c < V; c += 32) {
                     const float g = gr[c];
                     const float silu = g / (1.0f + expf(-g));
-                    orow[c] = from_f32<TO>(so[tok * V + c] * inv * norm_w[c] * silu * out_scale);
+                    orow[c] = from_f32<TO>(o[c] * inv * norm_w[c] * silu * out_scale);
                 }
             }
             __syncthreads();
@@ -193,7 +216,7 @@ __global__ void gla_scan_kernel(
 // allow at that R (a block's registers are threads x registers per thread, at most 65,536).
 static int gla_rows_per_thread(int D, int V, int* dg_out) {
     const int cands[4] = {8, 16, 32, 64};
-    const int limits[2][4] = {{512, 512, 512, 384}, {1024, 768, 640, 384}};
+    const int limits[2][4] = {{512, 512, 512, 384}, {1024, 768, 512, 384}};
     for (int pass = 0; pass < 2; ++pass)
         for (int c = 0; c < 4; ++c) {
             const int dg = (D + cands[c] - 1) / cands[c];
@@ -222,7 +245,7 @@ extern "C" int llm_gla_scan(
     int DG = 0;
     const int R = gla_rows_per_thread(D, V, &DG);
     if (R == 0) return LLM_REFUSED_SIZE;
-    const size_t smem = (static_cast<size_t>(GLA_TB) * (3 * D + 2 * V) + 2 * static_cast<size_t>(DG) * V) * sizeof(float);
+    const size_t smem = static_cast<size_t>(GLA_TB) * (3 * D + V + static_cast<size_t>(DG) * V) * sizeof(float);
     if (smem > 220 * 1024) return LLM_REFUSED_SIZE;
     cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
     const dim3 grid(num_items, H), block((V * DG + 31) / 32 * 32);

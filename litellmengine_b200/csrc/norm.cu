@@ -137,7 +137,7 @@ extern "C" int llm_rmsnorm(void* x, int x_dtype, const void* delta, int delta_dt
 // One block per row; y is float32 or bfloat16, `y_stride` elements from row to row.
 template <typename TY, typename TC>
 __global__ void rmsnorm_add_kernel(float* __restrict__ h, const TY* __restrict__ y, long long y_stride,
-                                   const float* __restrict__ w, TC* __restrict__ copy, int hidden, float eps) {
+                                   const float* __restrict__ w, TC* __restrict__ copy, int hidden, float eps, int vec) {
     pdl_begin();
     extern __shared__ __align__(16) float smem[];
     float* v = smem;
@@ -146,17 +146,40 @@ __global__ void rmsnorm_add_kernel(float* __restrict__ h, const TY* __restrict__
     float* hr = h + static_cast<size_t>(blockIdx.x) * hidden;
     TC* cr = copy ? copy + static_cast<size_t>(blockIdx.x) * hidden : nullptr;
     float ss = 0.0f;
-    for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
-        const float a = to_f32(yr[i]);
-        v[i] = a;
-        ss += a * a;
+    if (vec) {                                      // 8 elements per thread per trip, 16-byte accesses
+        for (int i = threadIdx.x * 8; i < hidden; i += blockDim.x * 8) {
+            float a[8];
+            load8(yr + i, a);
+#pragma unroll
+            for (int u = 0; u < 8; ++u) ss += a[u] * a[u];
+            store8(v + i, a);
+        }
+    } else {
+        for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+            const float a = to_f32(yr[i]);
+            v[i] = a;
+            ss += a * a;
+        }
     }
     const float total = block_sum(ss, scratch);
     const float inv = 1.0f / sqrtf(total / static_cast<float>(hidden) + eps);
-    for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
-        const float a = hr[i] + v[i] * inv * w[i];
-        hr[i] = a;
-        if (cr) cr[i] = from_f32<TC>(a);
+    if (vec) {
+        for (int i = threadIdx.x * 8; i < hidden; i += blockDim.x * 8) {
+            float a[8], b[8], g[8];
+            load8(v + i, a);
+            load8(hr + i, b);
+            load8(w + i, g);
+#pragma unroll
+            for (int u = 0; u < 8; ++u) b[u] += a[u] * inv * g[u];
+            store8(hr + i, b);
+            if (cr) store8(cr + i, b);
+        }
+    } else {
+        for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+            const float a = hr[i] + v[i] * inv * w[i];
+            hr[i] = a;
+            if (cr) cr[i] = from_f32<TC>(a);
+        }
     }
 }
 
@@ -169,6 +192,8 @@ extern "C" int llm_rmsnorm_add(float* h, const void* y, int y_dtype, long long y
     const int threads = hidden >= 4096 ? 512 : (hidden >= 1024 ? 256 : 128);
     cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
     if (!copy) copy_dtype = LLM_DT_F32;
+    const int vec = (hidden % 8 == 0) && (y_stride % 8 == 0) && aligned16(h) && aligned16(y) && aligned16(w) &&
+                    (!copy || aligned16(copy));
 #define LAUNCH(TY, TC)                                                                                           \
     do {                                                                                                         \
         auto kern = rmsnorm_add_kernel<TY, TC>;                                                                  \
@@ -178,7 +203,7 @@ extern "C" int llm_rmsnorm_add(float* h, const void* y, int y_dtype, long long y
             if (e != cudaSuccess) return static_cast<int>(e);                                                    \
         }                                                                                                        \
         launch_pdl(kern, dim3(num_rows), dim3(threads), smem, s, h, static_cast<const TY*>(y), y_stride, w,      \
-                   static_cast<TC*>(copy), hidden, eps);                                                         \
+                   static_cast<TC*>(copy), hidden, eps, vec);                                                    \
     } while (0)
     if (y_dtype == LLM_DT_F32 && copy_dtype == LLM_DT_F32) LAUNCH(float, float);
     else if (y_dtype == LLM_DT_F32 && copy_dtype == LLM_DT_BF16) LAUNCH(float, bf16);

@@ -25,10 +25,6 @@ def rms_norm(x, weight, eps):
     return rms_unit(x, eps) * weight
 
 
-def gelu_tanh(z):
-    return 0.5 * z * (1.0 + torch.tanh(math.sqrt(2.0 / math.pi) * (z + 0.044715 * z ** 3)))
-
-
 def sinusoid(positions, width, dtype=torch.float64):
     """[T, width]: entry 2i = sin(p * 10000^(-2i/width)), entry 2i+1 = cos of the same angle."""
     p = positions.to(torch.float64)[:, None]
@@ -154,3 +150,15 @@ def forward(ids, w, cfg, act=identity, dtype=torch.float64, return_layers=False)
 
 def bf16_round(x):
     return x.to(torch.bfloat16).to(x.dtype)
+
+
+def bf16_round_jittered(seed):
+    """Rounds to bfloat16 after a relative jitter of one bfloat16 rounding step: another computation of
+    the same values in bfloat16 (another summation order, another place of rounding) differs by as much.
+    Positions whose logits move a lot under it are ill conditioned in bfloat16, whoever computes them."""
+    g = torch.Generator().manual_seed(seed)
+
+    def act(x):
+        u = torch.rand(x.shape, generator=g, dtype=torch.float64) * 2.0 - 1.0
+        return (x * (1.0 + u * 2.0 ** -8)).to(torch.bfloat16).to(x.dtype)
+    return act

@@ -27,17 +27,45 @@ def model_of(case):
     return cfg, page, tm.random_weights(cfg, rank, seed)
 
 
-def plain_rows(cfg, w, reqs):
-    return {r: pt.forward(t, w, cfg).numpy() for r, t in reqs.items()}
+def _spread_error(row, ref_row, spread):
+    d = np.asarray(row, dtype=np.float64) - ref_row
+    return float(np.sqrt(np.mean((d - d.mean()) ** 2))) / spread
+
+
+class Reference:
+    """Whole-sequence logits of the plain code in double precision, and for each position the error that
+    rounding activations to bfloat16 alone causes there (the plain code run again with that rounding, and
+    with the rounding jittered by one step): where a sublayer's output is nearly zero (a linear-attention
+    head whose q . k cancels at a sequence's first tokens), the norm on it blows the rounding up, even
+    flips its sign, and no implementation in bfloat16 can be held to more than a few times that."""
+
+    def __init__(self, cfg, w, reqs, dtype):
+        self.rows = {r: pt.forward(t, w, cfg).numpy() for r, t in reqs.items()}
+        self.spread = float(np.sqrt(np.mean([np.var(v) for v in self.rows.values()])))
+        self.dtype = dtype
+        self.own = {}
+        if dtype == "bfloat16":
+            for r, t in reqs.items():
+                runs = [pt.forward(t, w, cfg, act=pt.bf16_round).numpy()]
+                runs += [pt.forward(t, w, cfg, act=pt.bf16_round_jittered(seed)).numpy() for seed in (1, 2, 3)]
+                self.own[r] = [max(_spread_error(x[p], self.rows[r][p], self.spread) for x in runs) for p in range(len(t))]
+
+    def limit(self, r, pos):
+        return max(LIMIT[self.dtype], 3.0 * self.own[r][pos]) if self.own else LIMIT[self.dtype]
+
+
+def plain_rows(cfg, w, reqs, dtype="float32"):
+    return Reference(cfg, w, reqs, dtype)
 
 
 def assert_close(got, ref, dtype, what):
     assert got, "nothing was compared"
-    spread = float(np.sqrt(np.mean([np.var(v) for v in ref.values()])))
+    held = 0
     for (r, pos) in sorted(got):
-        d = got[(r, pos)].astype(np.float64) - ref[r][pos]
-        err = float(np.sqrt(np.mean((d - d.mean()) ** 2))) / spread
-        assert err <= LIMIT[dtype], f"{what}: request {r} position {pos}: {err:.3e} > {LIMIT[dtype]:.1e}"
+        err, limit = _spread_error(got[(r, pos)], ref.rows[r][pos], ref.spread), ref.limit(r, pos)
+        assert err <= limit, f"{what}: request {r} position {pos}: {err:.3e} > {limit:.1e}"
+        held += limit <= 2 * LIMIT[dtype]
+    assert held >= 0.8 * len(got), "too few positions are well conditioned for this to be a test"
 
 
 def requests(cfg, lengths, seed):
@@ -50,7 +78,7 @@ def requests(cfg, lengths, seed):
 def test_every_cutting_matches_plain(case, dtype):
     cfg, page, w = model_of(case)
     reqs = requests(cfg, [1, 2, 3, 37, 90, 150], seed=1)
-    ref = plain_rows(cfg, w, reqs)
+    ref = plain_rows(cfg, w, reqs, dtype)
     for name, steps in (("whole", rh.trace_whole(reqs)), ("decode", rh.trace_tail_decode(reqs, tail=33)),
                         ("portions", rh.trace_portions(reqs, seed=2)),
                         ("mixed", rh.trace_mixed(reqs, seed=3, max_live=3))):
@@ -65,7 +93,7 @@ def test_long_prompt_takes_the_chunked_scan_and_agrees(dtype):
     token by token at the end, the single-pass kernel: all agree with the plain code."""
     cfg, page, w = model_of("C")
     reqs = requests(cfg, [700, 300], seed=4)
-    ref = plain_rows(cfg, w, reqs)
+    ref = plain_rows(cfg, w, reqs, dtype)
     for name, steps in (("whole", rh.trace_whole(reqs)), ("decode", rh.trace_tail_decode(reqs, tail=40)),
                         ("portions", rh.trace_portions(reqs, seed=5, sizes=(2, 61, 64, 65, 128, 257, 300)))):
         runner = rh.make_runner(cfg, w, dtype, page, rh.peak_tokens(steps, round_to=page), max_requests=2)
@@ -78,7 +106,7 @@ def test_long_decoding_under_graphs(dtype):
     replayed as a captured graph, the state moves on once per replay."""
     cfg, page, w = model_of("A")
     reqs = requests(cfg, [202, 180], seed=6)
-    ref = plain_rows(cfg, w, reqs)
+    ref = plain_rows(cfg, w, reqs, dtype)
     steps = [{"step": 0, "entries": [{"id": r, "tokens": t[:2], "want": [0, 1]} for r, t in reqs.items()], "end": []}]
     for k in range(2, 202):
         live = [(r, t) for r, t in reqs.items() if k < len(t)]
@@ -118,7 +146,7 @@ def test_greedy_generation_through_the_engine_and_scheduler():
         for _ in range(new):
             ids.append(int(pt.forward(ids, w, cfg)[-1].argmax()))
         want.append(ids[len(p):])
-    runner = rh.make_runner(cfg, w, "float32", page, 96, max_requests=3, max_tokens_per_step=32)
+    runner = rh.make_runner(cfg, w, "float32", page, 64, max_requests=3, max_tokens_per_step=32)
     engine = PagedGenerateEngine(runner, chunk=8)
     got = engine.generate(prompts, new)
     assert got == want
@@ -322,3 +350,61 @@ def test_recurrence_in_one_pass_in_portions_and_in_chunks(H, D, V):
         assert float(got[:, :2].abs().max()) == 0, what
         assert (s - s_ref).abs().max() < 2e-5 * max(1.0, float(s_ref.abs().max())), what
     assert s_ref[:, 0].abs().max() > 10 and s_ref[:, 1].abs().max() < 10        # the impulse is there, and is forgotten
+
+
+# ---- as a user runs it --------------------------------------------------------------------------------
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_trace_run_replays_a_model_folder(tmp_path, dtype):
+    """bin/trace_run on a folder with config.json and model.safetensors (bfloat16 tensors, the decay
+    projection's rank known from the tensors alone): a mixed trace with four live requests."""
+    import json
+    import os
+    import subprocess
+    from litellmengine_b200.weights import write_safetensors
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    cfg, page, w = model_of("B")
+    model_dir = tmp_path / "model"
+    model_dir.mkdir()
+    (model_dir / "config.json").write_text(json.dumps(cfg))
+    write_safetensors(str(model_dir / "model.safetensors"), {n: t.to(torch.bfloat16) for n, t in w.items()})
+    reqs = requests(cfg, [70, 33, 129, 1, 200], seed=8)
+    steps = rh.trace_mixed(reqs, seed=2, max_live=4)
+    out_dir = str(tmp_path / "out")
+    proc = subprocess.run(
+        [os.path.join(root, "bin", "trace_run"), "--model", str(model_dir), "--dtype", dtype, "--out", out_dir,
+         "--max-tokens", str(rh.peak_tokens(steps, 64)), "--max-requests", "4"],
+        input="".join(json.dumps(s) + "\n" for s in steps), capture_output=True, text=True, timeout=600)
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    assert proc.stdout.split("\n")[:-1] == [f"done {s['step']}" for s in steps]
+    got = {}
+    for s in steps:
+        wanted = sum(len(e["want"]) for e in s["entries"])
+        if wanted:
+            got[s["step"]] = np.fromfile(os.path.join(out_dir, f"{s['step']}.f32"), dtype="<f4").reshape(wanted, cfg["vocab"])
+    rows = rh.collect(steps, got)
+    assert len(rows) == sum(len(t) for t in reqs.values())
+    assert_close(rows, plain_rows(cfg, w, reqs, dtype), dtype, f"trace_run {dtype}")
+
+
+def test_command_line_generates_from_a_model_folder(tmp_path):
+    """The engine's command line picks the model class by config.json and generates greedily."""
+    import json
+    import os
+    import subprocess
+    import sys
+    from litellmengine_b200.weights import write_safetensors
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    cfg, page, w = model_of("A")
+    model_dir = tmp_path / "model"
+    model_dir.mkdir()
+    (model_dir / "config.json").write_text(json.dumps(cfg))
+    write_safetensors(str(model_dir / "model.safetensors"), {n: t.to(torch.bfloat16) for n, t in w.items()})
+    prompt = tm.random_tokens(cfg, 11, 77)
+    ids = list(prompt)
+    for _ in range(6):
+        ids.append(int(pt.forward(ids, w, cfg)[-1].argmax()))
+    proc = subprocess.run([sys.executable, os.path.join(root, "bin", "run_prompt"), "--model", str(model_dir), "--input-ids",
+                           ",".join(map(str, prompt)), "--max-tokens", "6", "--dtype", "float32"],
+                          capture_output=True, text=True, timeout=600)
+    assert proc.returncode == 0, proc.stdout[-2000:] + proc.stderr[-2000:]
+    assert proc.stdout.strip().split("\n")[-1] == ",".join(map(str, ids[len(prompt):]))
