@@ -9,7 +9,8 @@
 //
 // gla_decay_kernel   ln(alpha)[t, c] = ln(sigmoid(z)) / tau,  z = w2[c, :] . a[t, :] + b2[c]: the second
 //                    half of a low-rank decay projection, kept out of the matrix-product path so that its
-//                    input is never rounded.
+//                    input is never rounded.  A block takes 32 tokens x 128 channels and reads its slice
+//                    of the (transposed) weights once.
 // gla_scan_kernel    one block per (work item, head) walks the item's tokens in order.  Thread (dg, v)
 //                    keeps rows dg*R .. dg*R+R-1 of column v of the state in registers; tokens are
 //                    staged through shared memory sixteen at a time (no barrier between the tokens of a
@@ -34,30 +35,66 @@
 #define GLA_LOCAL 1
 #define GLA_OUT 2
 
+#define GLA_DECAY_TOKENS 32       // tokens a block of the decay kernel takes
+#define GLA_DECAY_CHANNELS 128    // and channels (one a thread)
+
+// w2t is the second half of the decay projection TRANSPOSED, [rank, channels]: thread c of a block reads
+// w2t[j][c] for every j once (neighbouring threads read neighbouring words) and applies it to all of the
+// block's tokens, whose inputs a[t][:] sit in shared memory.
 __global__ void gla_decay_kernel(const float* __restrict__ proj, long long stride, int a_off, int rank,
-                                 const float* __restrict__ w2, const float* __restrict__ b2, float inv_tau,
-                                 float* __restrict__ la, int channels) {
+                                 const float* __restrict__ w2t, const float* __restrict__ b2, float inv_tau,
+                                 float* __restrict__ la, int channels, int num_tokens) {
     pdl_begin();
-    extern __shared__ float a[];                    // [rank]
-    const size_t t = blockIdx.x;
-    for (int j = threadIdx.x; j < rank; j += blockDim.x) a[j] = proj[t * stride + a_off + j];
-    __syncthreads();
-    for (int c = threadIdx.x; c < channels; c += blockDim.x) {
-        const float* w = w2 + static_cast<size_t>(c) * rank;
-        float z = b2 ? b2[c] : 0.0f;
-        for (int j = 0; j < rank; ++j) z += w[j] * a[j];
-        // ln(sigmoid(z)) without overflow on either side
-        const float ls = z < 0.0f ? z - log1pf(expf(z)) : -log1pf(expf(-z));
-        la[t * channels + c] = ls * inv_tau;
+    extern __shared__ float a[];                    // [GLA_DECAY_TOKENS][rank]
+    const int t0 = blockIdx.x * GLA_DECAY_TOKENS;
+    const int nt = min(GLA_DECAY_TOKENS, num_tokens - t0);
+    for (int idx = threadIdx.x; idx < nt * rank; idx += blockDim.x) {
+        const int t = idx / rank, j = idx - t * rank;
+        a[idx] = proj[static_cast<size_t>(t0 + t) * stride + a_off + j];
     }
+    __syncthreads();
+    const int c = blockIdx.y * GLA_DECAY_CHANNELS + threadIdx.x;
+    if (c >= channels) return;
+    float z[GLA_DECAY_TOKENS];
+    const float bias = b2 ? b2[c] : 0.0f;
+#pragma unroll
+    for (int t = 0; t < GLA_DECAY_TOKENS; ++t) z[t] = bias;
+    int j = 0;
+    for (; j + 16 <= rank; j += 16) {              // sixteen weights in flight: a decode step's few blocks are bound by
+        float w[16];                                // the latency of these loads, not by their bytes
+#pragma unroll
+        for (int u = 0; u < 16; ++u) w[u] = w2t[static_cast<size_t>(j + u) * channels + c];
+#pragma unroll
+        for (int u = 0; u < 16; ++u)
+#pragma unroll
+            for (int t = 0; t < GLA_DECAY_TOKENS; ++t)
+                if (t < nt) z[t] += w[u] * a[t * rank + j + u];
+    }
+    for (; j < rank; ++j) {
+        const float w = w2t[static_cast<size_t>(j) * channels + c];
+#pragma unroll
+        for (int t = 0; t < GLA_DECAY_TOKENS; ++t)
+            if (t < nt) z[t] += w * a[t * rank + j];
+    }
+#pragma unroll
+    for (int t = 0; t < GLA_DECAY_TOKENS; ++t)
+        if (t < nt) {
+            // ln(sigmoid(z)) without overflow on either side
+            const float ls = z[t] < 0.0f ? z[t] - log1pf(expf(z[t])) : -log1pf(expf(-z[t]));
+            la[static_cast<size_t>(t0 + t) * channels + c] = ls * inv_tau;
+        }
 }
 
-extern "C" int llm_gla_decay(const float* proj, long long stride, int a_off, int rank, const float* w2, const float* b2,
+extern "C" int llm_gla_decay(const float* proj, long long stride, int a_off, int rank, const float* w2t, const float* b2,
                              float tau, float* la, int num_tokens, int channels, uintptr_t stream) {
     if (num_tokens <= 0) return LLM_OK;
-    if (rank <= 0 || channels <= 0 || !(tau > 0.0f) || rank > 8192) return LLM_REFUSED_SIZE;
-    launch_pdl(gla_decay_kernel, dim3(num_tokens), dim3(channels >= 256 ? 256 : 128), rank * sizeof(float),
-               reinterpret_cast<cudaStream_t>(stream), proj, stride, a_off, rank, w2, b2, 1.0f / tau, la, channels);
+    if (rank <= 0 || channels <= 0 || !(tau > 0.0f) || rank > 1024) return LLM_REFUSED_SIZE;
+    const dim3 grid((num_tokens + GLA_DECAY_TOKENS - 1) / GLA_DECAY_TOKENS,
+                    (channels + GLA_DECAY_CHANNELS - 1) / GLA_DECAY_CHANNELS);
+    if (grid.y > 65535) return LLM_REFUSED_SIZE;
+    launch_pdl(gla_decay_kernel, grid, dim3(GLA_DECAY_CHANNELS), GLA_DECAY_TOKENS * rank * sizeof(float),
+               reinterpret_cast<cudaStream_t>(stream), proj, stride, a_off, rank, w2t, b2, 1.0f / tau, la, channels,
+               num_tokens);
     return launch_status();
 }
 
@@ -291,12 +328,20 @@ __global__ void gla_chain_kernel(float* __restrict__ state, float* __restrict__ 
     const int d = e / V;
     float* st = state + (static_cast<size_t>(entry_slot[entry]) * H + h) * D * V + e;
     float S = *st;
-    for (int c = 0; c < n; ++c) {
-        const size_t at = static_cast<size_t>(first + c) * H + h;
-        float* cell = scratch_s + at * D * V + e;
-        const float L = *cell;
-        *cell = S;
-        S = scratch_a[at * D + d] * S + L;
+    for (int c0 = 0; c0 < n; c0 += 8) {              // eight chunks' loads in flight, then the chain through them
+        float L[8], A[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const size_t at = static_cast<size_t>(first + min(c0 + i, n - 1)) * H + h;
+            L[i] = scratch_s[at * D * V + e];
+            A[i] = scratch_a[at * D + d];
+        }
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+            if (c0 + i < n) {
+                scratch_s[(static_cast<size_t>(first + c0 + i) * H + h) * D * V + e] = S;
+                S = A[i] * S + L[i];
+            }
     }
     *st = S;
 }

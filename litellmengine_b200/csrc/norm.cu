@@ -134,10 +134,12 @@ extern "C" int llm_rmsnorm(void* x, int x_dtype, const void* delta, int delta_dt
 //     h[row] += y[row] * rsqrt(mean(y[row]^2) + eps) * w          (32-bit throughout; h is float32)
 // and, optionally, `copy[row]` = the new h[row] in the compute dtype: what the next sublayer of a
 // design reads whose sublayers take the stream itself (no norm in front of them).
-// One block per row; y is float32 or bfloat16, `y_stride` elements from row to row.
+// One block per row; y is float32 or bfloat16, `y_stride` elements from row to row.  y may come as the
+// `parts` k-splits of a product, `part_stride` elements apart, which are added up in order as they are read.
 template <typename TY, typename TC>
 __global__ void rmsnorm_add_kernel(float* __restrict__ h, const TY* __restrict__ y, long long y_stride,
-                                   const float* __restrict__ w, TC* __restrict__ copy, int hidden, float eps, int vec) {
+                                   const float* __restrict__ w, TC* __restrict__ copy, int hidden, float eps, int vec,
+                                   int parts, long long part_stride) {
     pdl_begin();
     extern __shared__ __align__(16) float smem[];
     float* v = smem;
@@ -150,13 +152,20 @@ __global__ void rmsnorm_add_kernel(float* __restrict__ h, const TY* __restrict__
         for (int i = threadIdx.x * 8; i < hidden; i += blockDim.x * 8) {
             float a[8];
             load8(yr + i, a);
+            for (int part = 1; part < parts; ++part) {
+                float b[8];
+                load8(yr + part * part_stride + i, b);
+#pragma unroll
+                for (int u = 0; u < 8; ++u) a[u] += b[u];
+            }
 #pragma unroll
             for (int u = 0; u < 8; ++u) ss += a[u] * a[u];
             store8(v + i, a);
         }
     } else {
         for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
-            const float a = to_f32(yr[i]);
+            float a = to_f32(yr[i]);
+            for (int part = 1; part < parts; ++part) a += to_f32(yr[part * part_stride + i]);
             v[i] = a;
             ss += a * a;
         }
@@ -184,16 +193,17 @@ __global__ void rmsnorm_add_kernel(float* __restrict__ h, const TY* __restrict__
 }
 
 extern "C" int llm_rmsnorm_add(float* h, const void* y, int y_dtype, long long y_stride, const float* w, void* copy,
-                               int copy_dtype, int num_rows, int hidden, float eps, uintptr_t stream) {
+                               int copy_dtype, int num_rows, int hidden, float eps, int parts, long long part_stride,
+                               uintptr_t stream) {
     if (num_rows <= 0) return LLM_OK;
-    if (hidden <= 0 || y_stride < hidden) return LLM_REFUSED_SIZE;
+    if (hidden <= 0 || y_stride < hidden || parts < 1) return LLM_REFUSED_SIZE;
     const size_t smem = (static_cast<size_t>((hidden + 7) & ~7) + 33) * sizeof(float);
     if (smem > 200 * 1024) return LLM_REFUSED_SIZE;
     const int threads = hidden >= 4096 ? 512 : (hidden >= 1024 ? 256 : 128);
     cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
     if (!copy) copy_dtype = LLM_DT_F32;
-    const int vec = (hidden % 8 == 0) && (y_stride % 8 == 0) && aligned16(h) && aligned16(y) && aligned16(w) &&
-                    (!copy || aligned16(copy));
+    const int vec = (hidden % 8 == 0) && (y_stride % 8 == 0) && (part_stride % 8 == 0) && aligned16(h) && aligned16(y) &&
+                    aligned16(w) && (!copy || aligned16(copy));
 #define LAUNCH(TY, TC)                                                                                           \
     do {                                                                                                         \
         auto kern = rmsnorm_add_kernel<TY, TC>;                                                                  \
@@ -203,7 +213,7 @@ extern "C" int llm_rmsnorm_add(float* h, const void* y, int y_dtype, long long y
             if (e != cudaSuccess) return static_cast<int>(e);                                                    \
         }                                                                                                        \
         launch_pdl(kern, dim3(num_rows), dim3(threads), smem, s, h, static_cast<const TY*>(y), y_stride, w,      \
-                   static_cast<TC*>(copy), hidden, eps, vec);                                                    \
+                   static_cast<TC*>(copy), hidden, eps, vec, parts, part_stride);                                \
     } while (0)
     if (y_dtype == LLM_DT_F32 && copy_dtype == LLM_DT_F32) LAUNCH(float, float);
     else if (y_dtype == LLM_DT_F32 && copy_dtype == LLM_DT_BF16) LAUNCH(float, bf16);

@@ -222,8 +222,12 @@ def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out_dtype: torch.
 def rmsnorm_add(h: torch.Tensor, y: torch.Tensor, weight: torch.Tensor, eps: float,
                 copy_dtype: Optional[torch.dtype] = None) -> Optional[torch.Tensor]:
     """h (float32, in place) += rmsnorm(y) * weight, row by row: a norm on a sublayer's output joined with
-    the residual add.  With `copy_dtype`, returns the new h in that dtype (what the next sublayer reads)."""
-    y = as_tensor(y)
+    the residual add.  With `copy_dtype`, returns the new h in that dtype (what the next sublayer reads).
+    y may be a `PartialSum`: the kernel adds the k-splits as it reads."""
+    parts, part_stride = 1, 0
+    if isinstance(y, PartialSum):
+        parts, part_stride = y.parts.shape[0], y.parts.stride(0)
+        y = y.parts[0]
     _dev(h, weight)
     if not y.is_cuda or y.dim() != 2 or y.stride(1) != 1:
         raise KernelError("y must be a CUDA matrix with unit stride along its rows")
@@ -232,9 +236,10 @@ def rmsnorm_add(h: torch.Tensor, y: torch.Tensor, weight: torch.Tensor, eps: flo
         raise KernelError("rmsnorm_add wants a float32 stream, a y of its shape and a float32 weight of the row length")
     copy = torch.empty((T, H), dtype=copy_dtype, device=h.device) if copy_dtype is not None else None
     f = _fn("norm", "llm_rmsnorm_add",
-            [c_void_p, c_void_p, c_int, c_longlong, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_void_p])
+            [c_void_p, c_void_p, c_int, c_longlong, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_int, c_longlong,
+             c_void_p])
     _check(f(_ptr(h), _ptr(y), _dt(y), y.stride(0), _ptr(weight), _ptr(copy), _dt(copy) if copy is not None else 0,
-             T, H, float(eps), _stream()), "rmsnorm_add")
+             T, H, float(eps), parts, part_stride, _stream()), "rmsnorm_add")
     return copy
 
 
@@ -518,17 +523,18 @@ def gla_supported(d: int, v: int) -> bool:
     return bool(_fn("linear_attention", "llm_gla_supported", [c_int, c_int])(d, v))
 
 
-def gla_decay(proj: torch.Tensor, a_off: int, rank: int, w2: torch.Tensor, b2: Optional[torch.Tensor],
+def gla_decay(proj: torch.Tensor, a_off: int, rank: int, w2t: torch.Tensor, b2: Optional[torch.Tensor],
               tau: float) -> torch.Tensor:
-    """ln(alpha) = ln(sigmoid(proj[:, a_off : a_off + rank] @ w2^T + b2)) / tau as float32 [T, channels]."""
-    _dev(w2, b2)
-    if proj.dtype != torch.float32 or proj.stride(1) != 1 or w2.dtype != torch.float32 or w2.shape[1] != rank:
-        raise KernelError("gla_decay wants a float32 projection and a float32 w2 [channels, rank]")
-    T, C = proj.shape[0], w2.shape[0]
+    """ln(alpha) = ln(sigmoid(proj[:, a_off : a_off + rank] @ w2t + b2)) / tau as float32 [T, channels];
+    `w2t` is the projection's second half transposed, float32 [rank, channels]."""
+    _dev(w2t, b2)
+    if proj.dtype != torch.float32 or proj.stride(1) != 1 or w2t.dtype != torch.float32 or w2t.shape[0] != rank:
+        raise KernelError("gla_decay wants a float32 projection and a float32 w2t [rank, channels]")
+    T, C = proj.shape[0], w2t.shape[1]
     la = torch.empty((T, C), dtype=torch.float32, device=proj.device)
     f = _fn("linear_attention", "llm_gla_decay",
             [c_void_p, c_longlong, c_int, c_int, c_void_p, c_void_p, c_float, c_void_p, c_int, c_int, c_void_p])
-    _check(f(_ptr(proj), proj.stride(0), a_off, rank, _ptr(w2), _ptr(b2), float(tau), _ptr(la), T, C, _stream()),
+    _check(f(_ptr(proj), proj.stride(0), a_off, rank, _ptr(w2t), _ptr(b2), float(tau), _ptr(la), T, C, _stream()),
            "gla_decay")
     return la
 

@@ -109,12 +109,13 @@ def branch_norm(block: Block, h: torch.Tensor, delta: Optional[torch.Tensor], ct
         x = held[1]
     else:
         x = h.to(narrow)
-    ctx.partials_ok = False
+    ctx.partials_ok = True                                      # the norm kernel adds a product's k-splits as it reads
     ctx.residual = None                                         # the norm stands between the product and the stream
     a = block.mixer.forward(x, ctx)
     x = block.mixer_norm.add_normed(h, a, narrow)
     if block.feed_forward is not None:
-        f = block.feed_forward.forward(x if narrow is not None else h)
+        extra = {"partials_ok": True} if getattr(block.feed_forward, "supports_partials", False) else {}
+        f = block.feed_forward.forward(x if narrow is not None else h, **extra)
         x = block.feed_forward_norm.add_normed(h, f, narrow)
     if narrow is not None:
         tables["stream_copy"] = (h, x)

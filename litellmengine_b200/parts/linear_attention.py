@@ -126,7 +126,8 @@ class GatedLinearAttention(BranchMixer):
         dt = torch.float32 if any(x.dtype == torch.float32 for x in rows) else rows[0].dtype
         self.w_in = torch.cat([x.to(dt) for x in rows], dim=0).contiguous()
         self.w_o = t[n["o"]].contiguous()
-        self.w2, self.b2 = t[n["a2"]].float().contiguous(), t[n["a2_bias"]].float().contiguous()
+        # the decay kernel reads the second half transposed, [rank, channels]
+        self.w2, self.b2 = t[n["a2"]].float().t().contiguous(), t[n["a2_bias"]].float().contiguous()
         self.norm_w = t[n["norm"]].float().contiguous()
         ops.prepare_streaming(self.w_in)
         ops.prepare_streaming(self.w_o)

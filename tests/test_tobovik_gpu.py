@@ -286,10 +286,10 @@ def test_attention_finds_one_far_key(far, dtype):
 
 def test_decay_is_sigmoid_to_the_power_one_over_tau():
     ops = _ops()
-    T, rank, C, tau = 9, 5, 48, 3.0
+    T, rank, C, tau = 71, 5, 300, 3.0
     proj = torch.randn(T, 11 + rank) * 4
     w2, b2 = torch.randn(C, rank) * 3, torch.randn(C) * 10          # z far out on both sides
-    la = ops.gla_decay(proj.to(DEV), 11, rank, w2.to(DEV), b2.to(DEV), tau)
+    la = ops.gla_decay(proj.to(DEV), 11, rank, w2.t().contiguous().to(DEV), b2.to(DEV), tau)
     z = proj[:, 11:].double() @ w2.double().T + b2.double()
     ref = torch.nn.functional.logsigmoid(z) / tau
     assert torch.isfinite(la).all()
