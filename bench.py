@@ -700,7 +700,9 @@ def design_bench(args, pk) -> int:
     slots = torch.arange(B, device=dev, dtype=torch.int32)
     dq0, dqn = torch.arange(B, device=dev, dtype=torch.int32), torch.ones(B, device=dev, dtype=torch.int32)
     args_d = (gp[:B], offs, la[:B], nw, 1e-5, D ** -0.5, 0.9, gout[:B], 0, state, slots, dq0, dqn)
-    add(f"gla_scan, {B} single tokens (new; reads and writes each state once)",
+    add(f"gla_step, {B} single tokens (new: the decode kernel; reads and writes each state once)",
+        lambda: ops.gla_step(*args_d[:-1], B, H, D, V), nbytes=2 * B * H * D * V * 4)
+    add(f"gla_scan, {B} single tokens (new: the general kernel on the same work)",
         lambda: ops.gla_scan(*args_d, None, B, ops.GLA_FULL, None, None, H, D, V), nbytes=2 * B * H * D * V * 4)
     print(json.dumps({"metric": "tokens/s of the Tobovik design beside Qwen3 at equal sizes (bfloat16, random weights)",
                       "design": "tobovik", "prompt_tokens": prompt_len, "decode_context": context, "steps": args.steps,

@@ -164,9 +164,7 @@ class TobovikConfig:
             blocks.append(BlockSpec(arrangement="branch_norm", mixer=mixer, feed_forward=ffn, mixer_norm=norm,
                                     feed_forward_norm=norm, weight_prefix=f"l{i}", mixer_norm_name="norm1",
                                     feed_forward_norm_name="norm2"))
-        for i, j in enumerate(owners):
-            if i != j and _comparable(layers[i]) != _comparable(layers[j]):
-                raise ConfigError(f"layers[{i}] runs the tensors of layer {j} but describes another layer")
+        # a layer that says `weights_of` runs its owner's mixer, feed-forward and norms: the owner's entry counts
         plan = ModelPlan(
             hidden_size=self.width, vocab_size=self.vocab, blocks=tuple(blocks),
             order=tuple(StageSpec(block=block_of[j]) for j in owners), final_norm=norm,
@@ -175,10 +173,6 @@ class TobovikConfig:
             embedding_position=PositionSpec(kind="sinusoid_added", theta=SINUSOID_BASE))
         plan.validate()
         return plan
-
-
-def _comparable(entry: Dict[str, Any]) -> Dict[str, Any]:
-    return {k: v for k, v in entry.items() if k != "weights_of"}
 
 
 def _freeze(x):

@@ -24,6 +24,7 @@
 //                      LOCAL  state in = 0, no outputs; the chunk's own contribution L and its total
 //                             decay A = prod alpha go to scratch
 //                      OUT    state in from scratch (what gla_chain_kernel put there), outputs only
+// gla_step_kernel    the same for entries of ONE token (decode steps): the state streams through, see there.
 // gla_chain_kernel   per (long entry, head), over its chunks in order: scratch[c] <- S (the state that
 //                    enters chunk c), S <- diag(A_c) S + L_c; at the end the slot's state <- S.
 //
@@ -310,6 +311,106 @@ extern "C" int llm_gla_scan(
     else return LLM_REFUSED_DTYPE;
 #undef BY_R
 #undef LAUNCH
+    return launch_status();
+}
+
+// The recurrence for entries that bring ONE token (decode steps): the state is streamed, not held: thread
+// (row group, column) walks its rows of the column once, eight loads in flight, S <- alpha S + k v written
+// back as it goes, its share of o left in shared memory; then a warp per 32 columns adds the shares and
+// applies norm, weight, gate and scale.  Few registers, so several blocks share an SM and the state's
+// bytes bound the kernel, as keys and values bound decode attention.  Entry i is row q_start[i].
+template <typename TO>
+__global__ void gla_step_kernel(
+    const float* __restrict__ proj, long long stride, int q_off, int k_off, int v_off, int g_off,
+    const float* __restrict__ la, const float* __restrict__ norm_w, float eps, float q_scale, float out_scale,
+    TO* __restrict__ out, long long out_stride, int out_off, float* __restrict__ state,
+    const int32_t* __restrict__ entry_slot, const int32_t* __restrict__ entry_q_start, int H, int D, int V, int DG) {
+    pdl_begin();
+    extern __shared__ __align__(16) float smem[];
+    float* sq = smem;                 // [D]
+    float* sk = sq + D;
+    float* sa = sk + D;
+    float* sv = sa + D;               // [V]
+    float* part = sv + V;             // [DG][V]
+    float* red = part + DG * V;       // 33
+    const int entry = blockIdx.x, h = blockIdx.y, tid = threadIdx.x;
+    const size_t row = static_cast<size_t>(entry_q_start[entry]);
+    const float* pr = proj + row * stride;
+    for (int d = tid; d < D; d += blockDim.x) {
+        sq[d] = pr[q_off + h * D + d] * q_scale;
+        sk[d] = pr[k_off + h * D + d];
+        sa[d] = expf(la[row * H * D + h * D + d]);
+    }
+    for (int c = tid; c < V; c += blockDim.x) sv[c] = pr[v_off + h * V + c];
+    __syncthreads();
+    const bool active = tid < V * DG;
+    const int c = active ? tid % V : 0, dg = active ? tid / V : 0;
+    const int rows = (D + DG - 1) / DG, d0 = dg * rows, d1 = min(D, d0 + rows);
+    float* S = state + (static_cast<size_t>(entry_slot[entry]) * H + h) * D * V + c;
+    if (active) {
+        const float vt = sv[c];
+        float p = 0.0f;
+        int d = d0;
+        for (; d + 8 <= d1; d += 8) {
+            float x[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) x[u] = S[static_cast<size_t>(d + u) * V];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                x[u] = sa[d + u] * x[u] + sk[d + u] * vt;
+                S[static_cast<size_t>(d + u) * V] = x[u];
+                p += x[u] * sq[d + u];
+            }
+        }
+        for (; d < d1; ++d) {
+            const float x = sa[d] * S[static_cast<size_t>(d) * V] + sk[d] * vt;
+            S[static_cast<size_t>(d) * V] = x;
+            p += x * sq[d];
+        }
+        part[dg * V + c] = p;
+    }
+    __syncthreads();
+    float ss = 0.0f;
+    for (int i = tid; i < V; i += blockDim.x) {
+        float o = part[i];
+        for (int g2 = 1; g2 < DG; ++g2) o += part[g2 * V + i];
+        part[i] = o;
+        ss += o * o;
+    }
+    const float total = block_sum(ss, red);
+    const float inv = 1.0f / sqrtf(total / static_cast<float>(V) + eps);
+    TO* orow = out + row * out_stride + out_off + h * V;
+    for (int i = tid; i < V; i += blockDim.x) {
+        const float g = pr[g_off + h * V + i];
+        orow[i] = from_f32<TO>(part[i] * inv * norm_w[i] * (g / (1.0f + expf(-g))) * out_scale);
+    }
+}
+
+extern "C" int llm_gla_step(
+    const float* proj, long long stride, int q_off, int k_off, int v_off, int g_off, const float* la,
+    const float* norm_w, float eps, float q_scale, float out_scale, void* out, int out_dtype, long long out_stride,
+    int out_off, float* state, const int32_t* entry_slot, const int32_t* entry_q_start, int num_entries, int H, int D,
+    int V, uintptr_t stream) {
+    if (num_entries <= 0) return LLM_OK;
+    if (H <= 0 || D <= 0 || V <= 0 || H > 65535 || V > 1024) return LLM_REFUSED_SIZE;
+    int DG = 256 / V;
+    if (DG < 1) DG = 1;
+    if (DG > D) DG = D;
+    const int threads = (V * DG + 31) / 32 * 32;
+    const size_t smem = (3 * static_cast<size_t>(D) + V + static_cast<size_t>(DG) * V + 33) * sizeof(float);
+    if (smem > 48 * 1024) return LLM_REFUSED_SIZE;
+    cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+    const dim3 grid(num_entries, H);
+    if (out_dtype == LLM_DT_F32)
+        launch_pdl((gla_step_kernel<float>), grid, dim3(threads), smem, s, proj, stride, q_off, k_off, v_off, g_off, la, norm_w,
+                   eps, q_scale, out_scale, static_cast<float*>(out), out_stride, out_off, state, entry_slot, entry_q_start,
+                   H, D, V, DG);
+    else if (out_dtype == LLM_DT_BF16)
+        launch_pdl((gla_step_kernel<bf16>), grid, dim3(threads), smem, s, proj, stride, q_off, k_off, v_off, g_off, la, norm_w,
+                   eps, q_scale, out_scale, static_cast<bf16*>(out), out_stride, out_off, state, entry_slot, entry_q_start,
+                   H, D, V, DG);
+    else
+        return LLM_REFUSED_DTYPE;
     return launch_status();
 }
 

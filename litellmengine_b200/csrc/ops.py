@@ -563,6 +563,25 @@ def gla_scan(proj: torch.Tensor, offs, la: torch.Tensor, norm_w: torch.Tensor, e
              _ptr(scratch_s), _ptr(scratch_a), H, D, V, _stream()), "gla_scan")
 
 
+def gla_step(proj: torch.Tensor, offs, la: torch.Tensor, norm_w: torch.Tensor, eps: float, q_scale: float,
+             out_scale: float, out: torch.Tensor, out_off: int, state: torch.Tensor, entry_slot, entry_q_start,
+             num_entries: int, H: int, D: int, V: int) -> None:
+    """`gla_scan` for a step whose entries all bring one token: the state is streamed through once instead
+    of being held, which is what a decode step wants (same arguments, same result up to summation order)."""
+    _dev(la, norm_w, state, entry_slot, entry_q_start)
+    if (proj.dtype != torch.float32 or proj.stride(1) != 1 or la.dtype != torch.float32 or state.dtype != torch.float32
+            or tuple(state.shape[1:]) != (H, D, V) or norm_w.dtype != torch.float32 or norm_w.numel() != V
+            or out.stride(1) != 1):
+        raise KernelError("gla_step: float32 projection, decays and state [slots, H, D, V]; norm weight [V]")
+    q_off, k_off, v_off, g_off = offs
+    f = _fn("linear_attention", "llm_gla_step",
+            [c_void_p, c_longlong, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_float, c_float, c_float, c_void_p,
+             c_int, c_longlong, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p])
+    _check(f(_ptr(proj), proj.stride(0), q_off, k_off, v_off, g_off, _ptr(la), _ptr(norm_w), float(eps),
+             float(q_scale), float(out_scale), _ptr(out), _dt(out), out.stride(0), out_off, _ptr(state),
+             _ptr(entry_slot), _ptr(entry_q_start), num_entries, H, D, V, _stream()), "gla_step")
+
+
 def gla_chain(state: torch.Tensor, scratch_s: torch.Tensor, scratch_a: torch.Tensor, chains: torch.Tensor,
               num_chains: int, entry_slot, H: int, D: int, V: int) -> None:
     """Per (chain, head): walk the chain's chunks in order, leaving in scratch_s[c] the state that enters

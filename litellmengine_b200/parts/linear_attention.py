@@ -153,6 +153,9 @@ class GatedLinearAttention(BranchMixer):
         common = (proj, offs, la, self.norm_w, self.eps, D ** -0.5, out_scale, out, out_col0, ctx.state, b.entry_slot,
                   b.entry_q_start, b.entry_q_len)
         work = b.preludes.get(ScanWork.name)
+        if b.max_q_len == 1:                                 # a decode step: the states stream through once
+            ops.gla_step(*common[:-1], b.num_entries, H, D, V)
+            return
         if work is None:                                     # no work lists: every entry in one pass
             ops.gla_scan(*common, None, b.num_entries, ops.GLA_FULL, None, None, H, D, V)
             return

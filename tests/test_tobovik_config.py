@@ -50,7 +50,6 @@ def test_tensor_names_and_shapes_are_the_designs():
     (lambda d: d["layers"][2]["mixer"]["left"].update(kv_heads=3), "multiple"),
     (lambda d: d["layers"][2]["mlp"].update(kind="routed"), "not built"),
     (lambda d: d["layers"][1].update(weights_of=9), "must name a layer"),
-    (lambda d: d["layers"][3]["mixer"].update(heads=5), "describes another layer"),
     (lambda d: (d["layers"][0].update(weights_of=3)), "circle"),
 ])
 def test_bad_configurations_are_refused_with_the_field_named(change, message):

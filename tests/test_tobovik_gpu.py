@@ -16,7 +16,8 @@ pytestmark = pytest.mark.gpu
 DEV = "cuda:0"
 
 CASES = {"A": (tm.TOBO_A, tm.TOBO_A_PAGE, tm.TOBO_A_RANK, 3), "B": (tm.TOBO_B, tm.TOBO_B_PAGE, tm.TOBO_B_RANK, 5),
-         "C": (tm.TOBO_C, tm.TOBO_C_PAGE, tm.TOBO_C_RANK, 9)}
+         "C": (tm.TOBO_C, tm.TOBO_C_PAGE, tm.TOBO_C_RANK, 9), "D": (tm.TOBO_D, tm.TOBO_D_PAGE, tm.TOBO_D_RANK, 11),
+         "E": (tm.TOBO_E, tm.TOBO_E_PAGE, tm.TOBO_E_RANK, 13)}
 # root mean square over the vocabulary of (difference minus its mean), as a fraction of the reference
 # logits' spread; the float32 run is measured against the plain code in double precision
 LIMIT = {"float32": 1e-4, "bfloat16": 0.12}
@@ -74,7 +75,7 @@ def requests(cfg, lengths, seed):
 
 # ---- whole models, every cutting ------------------------------------------------------------------
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("case", ["A", "B", "C"])
+@pytest.mark.parametrize("case", ["A", "B", "C", "D", "E"])
 def test_every_cutting_matches_plain(case, dtype):
     cfg, page, w = model_of(case)
     reqs = requests(cfg, [1, 2, 3, 37, 90, 150], seed=1)
@@ -300,7 +301,8 @@ def test_decay_is_sigmoid_to_the_power_one_over_tau():
 def test_recurrence_in_one_pass_in_portions_and_in_chunks(H, D, V):
     """The recurrence kernel against the token-by-token recurrence in double precision: an entry in one
     pass; the same tokens in portions that carry the state in the request's slot (down to one token); cut
-    into chunks that run side by side (local pass, chain, output pass).  A channel that never decays
+    into chunks that run side by side (local pass, chain, output pass); token by token through the kernel
+    of decode steps.  A channel that never decays
     carries an impulse from the first token to the last; a channel that decays at once forgets it."""
     ops = _ops()
     T, eps, out_scale = 333, 1e-5, 0.9
@@ -319,7 +321,7 @@ def test_recurrence_in_one_pass_in_portions_and_in_chunks(H, D, V):
     ref = (pt.rms_norm(o_ref, norm_w.double(), eps) * (gt * torch.sigmoid(gt)) * out_scale).reshape(T, -1)
     slots = _i32([2])
 
-    def run(cuts, chunk=None):
+    def run(cuts, chunk=None, step=False):
         state = torch.zeros((4, H, D, V), dtype=torch.float32, device=DEV)
         state[1] = 7.0                                                    # another request's state stays untouched
         out = torch.zeros((T, H * V + 4), dtype=torch.float32, device=DEV)
@@ -328,7 +330,9 @@ def test_recurrence_in_one_pass_in_portions_and_in_chunks(H, D, V):
         for n in cuts:
             args = (pd[at:at + n], offs, lad[at:at + n], nw, eps, D ** -0.5, out_scale, out[at:at + n], 2, state, slots,
                     _i32([0]), _i32([n]))
-            if chunk is None:
+            if step and n == 1:
+                ops.gla_step(*args[:-1], 1, H, D, V)
+            elif chunk is None:
                 ops.gla_scan(*args, None, 1, ops.GLA_FULL, None, None, H, D, V)
             else:
                 items = [(0, c, min(chunk, n - c), i) for i, c in enumerate(range(0, n, chunk))]
@@ -345,7 +349,8 @@ def test_recurrence_in_one_pass_in_portions_and_in_chunks(H, D, V):
 
     scale = max(1.0, float(ref.abs().max()))
     for what, (got, s) in (("one pass", run([T])), ("portions", run([1, 2, 16, 17, 1, 64, 100, 31, 101])),
-                           ("chunks", run([T], chunk=64)), ("chunks after a portion", run([70, T - 70], chunk=32))):
+                           ("chunks", run([T], chunk=64)), ("chunks after a portion", run([70, T - 70], chunk=32)),
+                           ("a portion, then the decode kernel token by token", run([33] + [1] * (T - 33), step=True))):
         assert (got[:, 2:2 + H * V] - ref).abs().max() < 2e-5 * scale, what
         assert float(got[:, :2].abs().max()) == 0, what
         assert (s - s_ref).abs().max() < 2e-5 * max(1.0, float(s_ref.abs().max())), what

@@ -65,6 +65,16 @@ TOBO_C = _config(211, 64, 1e-5, [_C_PAR, _gla(2, 16, 32, 16.0, 96), _shared(_C_P
 TOBO_C_PAGE, TOBO_C_RANK = 16, 8
 
 
+# D: head size 128 with keys and values alike: a bfloat16 run takes the tcgen05 prompt kernel and the TMA decode kernel
+_D_PAR = _parallel(_left(4, 2, 128, 128, coef=0.5, every=16), _right(1, 64, 128, 4.0), 1.0, 0.6, 80)
+TOBO_D = _config(157, 96, 1e-5, [_D_PAR, _shared(_D_PAR, 0)])
+TOBO_D_PAGE, TOBO_D_RANK = 16, 4
+
+# E: linear attention only: a model without pages
+TOBO_E = _config(89, 32, 1e-6, [_gla(2, 16, 16, 2.0, 48), _gla(1, 32, 8, 32.0, 0), _shared(_gla(2, 16, 16, 2.0, 48), 0)])
+TOBO_E_PAGE, TOBO_E_RANK = 8, 5
+
+
 def num_owner_layers(cfg) -> list:
     return [i for i, e in enumerate(cfg["layers"]) if e.get("weights_of") is None]
 
