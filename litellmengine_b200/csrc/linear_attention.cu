@@ -101,8 +101,8 @@ extern "C" int llm_gla_decay(const float* proj, long long stride, int a_off, int
 
 // items: int32 [n, 4] = (entry, first row in the batch, tokens, index of the item's scratch) or null: item i
 // is entry i, all of it.
-template <int R, typename TO>
-__global__ void gla_scan_kernel(
+template <int R, int MAX_THREADS, typename TO>
+__global__ void __launch_bounds__(MAX_THREADS) gla_scan_kernel(
     const float* __restrict__ proj, long long stride, int q_off, int k_off, int v_off, int g_off,
     const float* __restrict__ la, const float* __restrict__ norm_w, float eps, float q_scale, float out_scale,
     TO* __restrict__ out, long long out_stride, int out_off, float* __restrict__ state,
@@ -249,26 +249,38 @@ __global__ void gla_scan_kernel(
     }
 }
 
-// Rows of a state column that one thread keeps (R), and the row groups DG = ceil(D / R): the smallest R
-// whose block of V * DG threads fits, first within 512 threads, then within what the kernel's registers
-// allow at that R (a block's registers are threads x registers per thread, at most 65,536).
-static int gla_rows_per_thread(int D, int V, int* dg_out) {
+// Rows of a state column that one thread keeps (R), the row groups DG = ceil(D / R), and the block size the
+// kernel is compiled for: the smallest R whose block of V * DG threads fits, first within 512 threads,
+// then within what the kernel's registers allow at that R (a block's registers are threads x registers
+// per thread, at most 65,536).  States too large for that (128 x 256 a head and more) take R = 64 compiled
+// for 512 or 1,024 threads: the compiler then keeps part of the state in local memory, which is slow and
+// correct.
+static int gla_rows_per_thread(int D, int V, int* dg_out, int* max_threads) {
     const int cands[4] = {8, 16, 32, 64};
     const int limits[2][4] = {{512, 512, 512, 384}, {1024, 768, 512, 384}};
+    const int compiled_for[4] = {1024, 768, 512, 384};
     for (int pass = 0; pass < 2; ++pass)
         for (int c = 0; c < 4; ++c) {
             const int dg = (D + cands[c] - 1) / cands[c];
             if (static_cast<long long>(V) * dg <= limits[pass][c]) {
                 *dg_out = dg;
+                *max_threads = compiled_for[c];
                 return cands[c];
             }
+        }
+    const int dg = (D + 63) / 64;
+    for (int limit = 512; limit <= 1024; limit *= 2)
+        if (static_cast<long long>(V) * dg <= limit) {
+            *dg_out = dg;
+            *max_threads = limit;
+            return 64;
         }
     return 0;
 }
 
 extern "C" int llm_gla_supported(int D, int V) {
-    int dg;
-    return (D > 0 && V > 0 && gla_rows_per_thread(D, V, &dg) > 0) ? 1 : 0;
+    int dg, mt;
+    return (D > 0 && V > 0 && gla_rows_per_thread(D, V, &dg, &mt) > 0) ? 1 : 0;
 }
 
 extern "C" int llm_gla_scan(
@@ -280,16 +292,16 @@ extern "C" int llm_gla_scan(
     if (num_items <= 0) return LLM_OK;
     if (H <= 0 || D <= 0 || V <= 0 || mode < 0 || mode > 2 || H > 65535) return LLM_REFUSED_SIZE;
     if (mode != GLA_FULL && (!items || !scratch_s || !scratch_a)) return LLM_REFUSED_SIZE;
-    int DG = 0;
-    const int R = gla_rows_per_thread(D, V, &DG);
+    int DG = 0, MT = 0;
+    const int R = gla_rows_per_thread(D, V, &DG, &MT);
     if (R == 0) return LLM_REFUSED_SIZE;
     const size_t smem = static_cast<size_t>(GLA_TB) * (3 * D + V + static_cast<size_t>(DG) * V) * sizeof(float);
     if (smem > 220 * 1024) return LLM_REFUSED_SIZE;
     cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
     const dim3 grid(num_items, H), block((V * DG + 31) / 32 * 32);
-#define LAUNCH(RR, TO)                                                                                            \
+#define LAUNCH(RR, MM, TO)                                                                                        \
     do {                                                                                                          \
-        auto kern = gla_scan_kernel<RR, TO>;                                                                      \
+        auto kern = gla_scan_kernel<RR, MM, TO>;                                                                    \
         if (smem > 48 * 1024) {                                                                                   \
             const cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,         \
                                                        static_cast<int>(smem));                                   \
@@ -301,10 +313,14 @@ extern "C" int llm_gla_scan(
     } while (0)
 #define BY_R(TO)                                                                                                  \
     switch (R) {                                                                                                  \
-        case 8: LAUNCH(8, TO); break;                                                                             \
-        case 16: LAUNCH(16, TO); break;                                                                           \
-        case 32: LAUNCH(32, TO); break;                                                                           \
-        default: LAUNCH(64, TO); break;                                                                           \
+        case 8: LAUNCH(8, 1024, TO); break;                                                                       \
+        case 16: LAUNCH(16, 768, TO); break;                                                                      \
+        case 32: LAUNCH(32, 512, TO); break;                                                                      \
+        default:                                                                                                  \
+            if (MT == 384) LAUNCH(64, 384, TO);                                                                   \
+            else if (MT == 512) LAUNCH(64, 512, TO);                                                              \
+            else LAUNCH(64, 1024, TO);                                                                            \
+            break;                                                                                                \
     }
     if (out_dtype == LLM_DT_F32) { BY_R(float) }
     else if (out_dtype == LLM_DT_BF16) { BY_R(bf16) }

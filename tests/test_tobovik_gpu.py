@@ -297,7 +297,8 @@ def test_decay_is_sigmoid_to_the_power_one_over_tau():
     assert ((la.double().cpu() - ref).abs() / (1 + ref.abs())).max() < 1e-5
 
 
-@pytest.mark.parametrize("H,D,V", [(2, 8, 16), (3, 16, 8), (2, 24, 40), (1, 64, 64), (2, 128, 128), (1, 48, 100)])
+@pytest.mark.parametrize("H,D,V", [(2, 8, 16), (3, 16, 8), (2, 24, 40), (1, 64, 64), (2, 128, 128), (1, 48, 100),
+                                   (1, 128, 256)])
 def test_recurrence_in_one_pass_in_portions_and_in_chunks(H, D, V):
     """The recurrence kernel against the token-by-token recurrence in double precision: an entry in one
     pass; the same tokens in portions that carry the state in the request's slot (down to one token); cut
