@@ -60,13 +60,13 @@ TOBO_B = _config(131, 48, 3e-6, [_B_PAR0, _B_PAR1, _gla(2, 32, 48, 8.0, 64), _sh
 TOBO_B_PAGE, TOBO_B_RANK = 16, 3
 
 # C: head size 64 with keys and values alike (a bfloat16 run takes the tuned attention kernels), longer sequences
-_C_PAR = _parallel(_left(4, 2, 64, 64, coef=0.2, every=32), _right(2, 32, 64, 16.0), 0.9, 0.8, 96)
+_C_PAR = _parallel(_left(4, 2, 64, 64, coef=0.2, every=32, scale=0.09), _right(2, 32, 64, 16.0), 0.9, 0.8, 96)
 TOBO_C = _config(211, 64, 1e-5, [_C_PAR, _gla(2, 16, 32, 16.0, 96), _shared(_C_PAR, 0)])
 TOBO_C_PAGE, TOBO_C_RANK = 16, 8
 
 
 # D: head size 128 with keys and values alike: a bfloat16 run takes the tcgen05 prompt kernel and the TMA decode kernel
-_D_PAR = _parallel(_left(4, 2, 128, 128, coef=0.5, every=16), _right(1, 64, 128, 4.0), 1.0, 0.6, 80)
+_D_PAR = _parallel(_left(4, 2, 128, 128, coef=0.5, every=16, scale=0.11), _right(1, 64, 128, 4.0), 1.0, 0.6, 80)
 TOBO_D = _config(157, 96, 1e-5, [_D_PAR, _shared(_D_PAR, 0)])
 TOBO_D_PAGE, TOBO_D_RANK = 16, 4
 
