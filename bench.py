@@ -677,7 +677,7 @@ def design_bench(args, pk) -> int:
     # the recurrence: prompt portion (chunks side by side) and single decoded tokens
     H, D, V = heads // 4, d, d
     gp = torch.randn(T, 2 * H * D + 2 * H * V, device=dev)
-    la = -torch.rand(T, H * D, device=dev) * 0.1
+    la = torch.exp(-torch.rand(T, H * D, device=dev) * 0.1)          # the decays
     nw = torch.ones(V, device=dev)
     offs = (0, H * D, 2 * H * D, 2 * H * D + H * V)
     gout = torch.empty(T, H * V, device=dev, dtype=torch.bfloat16)

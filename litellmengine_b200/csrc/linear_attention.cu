@@ -7,7 +7,7 @@
 // recurrence's operands must not be rounded to 16 bits, so this is no tensor-core kernel; its roofline
 // is the float32 FMA rate for prompt portions and the state's bytes for single decoded tokens).
 //
-// gla_decay_kernel   ln(alpha)[t, c] = ln(sigmoid(z)) / tau,  z = w2[c, :] . a[t, :] + b2[c]: the second
+// gla_decay_kernel   alpha[t, c] = exp(ln(sigmoid(z)) / tau),  z = w2[c, :] . a[t, :] + b2[c]: the second
 //                    half of a low-rank decay projection, kept out of the matrix-product path so that its
 //                    input is never rounded.  A block takes 32 tokens x 128 channels and reads its slice
 //                    of the (transposed) weights once.
@@ -82,7 +82,7 @@ __global__ void gla_decay_kernel(const float* __restrict__ proj, long long strid
         if (t < nt) {
             // ln(sigmoid(z)) without overflow on either side
             const float ls = z[t] < 0.0f ? z[t] - log1pf(expf(z[t])) : -log1pf(expf(-z[t]));
-            la[static_cast<size_t>(t0 + t) * channels + c] = ls * inv_tau;
+            la[static_cast<size_t>(t0 + t) * channels + c] = expf(ls * inv_tau);      // alpha = sigmoid(z)^(1/tau)
         }
 }
 
@@ -99,16 +99,21 @@ extern "C" int llm_gla_decay(const float* proj, long long stride, int a_off, int
     return launch_status();
 }
 
+__device__ __forceinline__ void gla_cp16(float* smem_dst, const float* src) {
+    const unsigned d = static_cast<unsigned>(__cvta_generic_to_shared(smem_dst));
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(d), "l"(src));
+}
+
 // items: int32 [n, 4] = (entry, first row in the batch, tokens, index of the item's scratch) or null: item i
-// is entry i, all of it.
+// is entry i, all of it.  `alpha` [T, H*D] are the decays themselves (what gla_decay_kernel writes).
 template <int R, int MAX_THREADS, typename TO>
 __global__ void __launch_bounds__(MAX_THREADS) gla_scan_kernel(
     const float* __restrict__ proj, long long stride, int q_off, int k_off, int v_off, int g_off,
-    const float* __restrict__ la, const float* __restrict__ norm_w, float eps, float q_scale, float out_scale,
+    const float* __restrict__ alpha, const float* __restrict__ norm_w, float eps, float q_scale, float out_scale,
     TO* __restrict__ out, long long out_stride, int out_off, float* __restrict__ state,
     const int32_t* __restrict__ entry_slot, const int32_t* __restrict__ entry_q_start,
     const int32_t* __restrict__ entry_q_len, const int32_t* __restrict__ items, int mode,
-    float* __restrict__ scratch_s, float* __restrict__ scratch_a, int H, int D, int V, int DG) {
+    float* __restrict__ scratch_s, float* __restrict__ scratch_a, int H, int D, int V, int DG, int vec) {
     pdl_begin();
     extern __shared__ __align__(16) float smem[];
     const int h = blockIdx.y;
@@ -129,11 +134,10 @@ __global__ void __launch_bounds__(MAX_THREADS) gla_scan_kernel(
     // thread (dg, v) for tid < V * DG; the block is rounded up to whole warps and the rest only help to stage
     const bool active = tid < V * DG;
     const int v = active ? tid % V : 0, dg = active ? tid / V : 0;
-    float* sq = smem;                               // [TB][D]
-    float* sk = sq + GLA_TB * D;
-    float* sa = sk + GLA_TB * D;
-    float* sv = sa + GLA_TB * D;                    // [TB][V]
-    float* part = sv + GLA_TB * V;                  // [TB][DG][V]: each row group's share of o, added up in the epilogue
+    // two staging buffers of [TB][D] queries, keys, decays and [TB][V] values: batch b+1 is copied in
+    // (cp.async, sixteen bytes at a time) while batch b is worked on
+    const int buf_floats = GLA_TB * (3 * D + V);
+    float* part = smem + 2 * buf_floats;            // [TB][DG][V]: each row group's share of o, added up in the epilogue
     const size_t HD = static_cast<size_t>(H) * D;
     const bool outputs = mode != GLA_LOCAL;
     // a thread whose R rows all exist reads its decays, keys and queries sixteen bytes at a time
@@ -149,21 +153,57 @@ __global__ void __launch_bounds__(MAX_THREADS) gla_scan_kernel(
         S[r] = (s_in && active && d < D) ? s_in[static_cast<size_t>(d) * V + v] : 0.0f;
     }
 
-    for (int done = 0; done < count; done += GLA_TB) {
+    auto stage = [&](int done, int buf) {
         const int nb = min(GLA_TB, count - done);
         const size_t base = static_cast<size_t>(row0 + done);
-        for (int idx = tid; idx < nb * D; idx += nthreads) {
-            const int tok = idx / D, d = idx - tok * D;
-            const float* pr = proj + (base + tok) * stride + h * D + d;
-            sk[idx] = pr[k_off];
-            sa[idx] = expf(la[(base + tok) * HD + h * D + d]);
-            if (outputs) sq[idx] = pr[q_off] * q_scale;
+        float* bq = smem + buf * buf_floats;
+        float* bk = bq + GLA_TB * D;
+        float* ba = bk + GLA_TB * D;
+        float* bv = ba + GLA_TB * D;
+        if (vec) {
+            const int d4 = D >> 2, v4 = V >> 2;
+            for (int idx = tid; idx < nb * d4; idx += nthreads) {
+                const int tok = idx / d4, c = (idx - tok * d4) << 2;
+                const float* pr = proj + (base + tok) * stride + h * D + c;
+                gla_cp16(bk + tok * D + c, pr + k_off);
+                gla_cp16(ba + tok * D + c, alpha + (base + tok) * HD + h * D + c);
+                if (outputs) gla_cp16(bq + tok * D + c, pr + q_off);
+            }
+            for (int idx = tid; idx < nb * v4; idx += nthreads) {
+                const int tok = idx / v4, c = (idx - tok * v4) << 2;
+                gla_cp16(bv + tok * V + c, proj + (base + tok) * stride + v_off + h * V + c);
+            }
+            asm volatile("cp.async.commit_group;\n" ::);
+        } else {
+            for (int idx = tid; idx < nb * D; idx += nthreads) {
+                const int tok = idx / D, d = idx - tok * D;
+                const float* pr = proj + (base + tok) * stride + h * D + d;
+                bk[idx] = pr[k_off];
+                ba[idx] = alpha[(base + tok) * HD + h * D + d];
+                if (outputs) bq[idx] = pr[q_off];
+            }
+            for (int idx = tid; idx < nb * V; idx += nthreads) {
+                const int tok = idx / V, c = idx - tok * V;
+                bv[idx] = proj[(base + tok) * stride + v_off + h * V + c];
+            }
         }
-        for (int idx = tid; idx < nb * V; idx += nthreads) {
-            const int tok = idx / V, c = idx - tok * V;
-            sv[idx] = proj[(base + tok) * stride + v_off + h * V + c];
+    };
+
+    stage(0, 0);
+    for (int done = 0, b = 0; done < count; done += GLA_TB, ++b) {
+        const int nb = min(GLA_TB, count - done);
+        const size_t base = static_cast<size_t>(row0 + done);
+        const bool more = done + GLA_TB < count;
+        if (more) stage(done + GLA_TB, (b + 1) & 1);
+        if (vec) {
+            if (more) asm volatile("cp.async.wait_group 1;\n" ::: "memory");
+            else asm volatile("cp.async.wait_group 0;\n" ::: "memory");
         }
         __syncthreads();
+        const float* sq = smem + (b & 1) * buf_floats;
+        const float* sk = sq + GLA_TB * D;
+        const float* sa = sk + GLA_TB * D;
+        const float* sv = sa + GLA_TB * D;
         for (int tok = 0; tok < nb; ++tok) {
             const float vt = sv[tok * V + v];
             const float* a = sa + tok * D + dg * R;
@@ -217,6 +257,7 @@ __global__ void __launch_bounds__(MAX_THREADS) gla_scan_kernel(
                 for (int c = lane; c < V; c += 32) {
                     float sum = o[c];
                     for (int g2 = 1; g2 < DG; ++g2) sum += o[g2 * V + c];
+                    sum *= q_scale;                 // q = W_q x * q_scale, applied to the finished sum
                     o[c] = sum;
                     ss += sum * sum;
                 }
@@ -230,8 +271,8 @@ __global__ void __launch_bounds__(MAX_THREADS) gla_scan_kernel(
                     orow[c] = from_f32<TO>(o[c] * inv * norm_w[c] * silu * out_scale);
                 }
             }
-            __syncthreads();
         }
+        __syncthreads();                            // this buffer is filled again two batches on
     }
     if (mode == GLA_OUT) return;
     float* s_out = mode == GLA_FULL ? slot_state : scratch_s + (static_cast<size_t>(sidx) * H + h) * D * V;
@@ -242,25 +283,39 @@ __global__ void __launch_bounds__(MAX_THREADS) gla_scan_kernel(
     }
     if (mode == GLA_LOCAL) {                        // the chunk's total decay per key channel
         for (int d = tid; d < D; d += nthreads) {
-            float sum = 0.0f;
-            for (int tok = 0; tok < count; ++tok) sum += la[(static_cast<size_t>(row0) + tok) * HD + h * D + d];
-            scratch_a[(static_cast<size_t>(sidx) * H + h) * D + d] = expf(sum);
+            float prod = 1.0f;
+            for (int tok = 0; tok < count; ++tok) prod *= alpha[(static_cast<size_t>(row0) + tok) * HD + h * D + d];
+            scratch_a[(static_cast<size_t>(sidx) * H + h) * D + d] = prod;
         }
     }
 }
 
 // Rows of a state column that one thread keeps (R), the row groups DG = ceil(D / R), and the block size the
-// kernel is compiled for: the smallest R whose block of V * DG threads fits, first within 512 threads,
-// then within what the kernel's registers allow at that R (a block's registers are threads x registers
+// kernel is compiled for: 16, else 32, else 64, else 8 rows, whichever block of V * DG threads fits first
+// within 512 threads (64 x 64 a head: 110 us with 16 rows, 134 with 8, 173 with 32 for 2,048 tokens of 16
+// heads; 128 x 128: 32 rows, 185 us for 8 heads), then within what the kernel's registers allow at that R (a block's registers are threads x registers
 // per thread, at most 65,536).  States too large for that (128 x 256 a head and more) take R = 64 compiled
 // for 512 or 1,024 threads: the compiler then keeps part of the state in local memory, which is slow and
 // correct.
 static int gla_rows_per_thread(int D, int V, int* dg_out, int* max_threads) {
     const int cands[4] = {8, 16, 32, 64};
-    const int limits[2][4] = {{512, 512, 512, 384}, {1024, 768, 512, 384}};
-    const int compiled_for[4] = {1024, 768, 512, 384};
+    const int limits[2][4] = {{512, 512, 512, 384}, {1024, 1024, 512, 384}};
+    const int compiled_for[4] = {1024, 1024, 512, 384};
+    static int forced = -1;                        // LLM_GLA_ROWS=8|16|32|64: take that R when its block fits (for measurements)
+    if (forced < 0) {
+        const char* e = getenv("LLM_GLA_ROWS");
+        forced = e ? atoi(e) : 0;
+    }
+    for (int c = 0; c < 4; ++c)
+        if (forced == cands[c] && static_cast<long long>(V) * ((D + forced - 1) / forced) <= limits[1][c]) {
+            *dg_out = (D + forced - 1) / forced;
+            *max_threads = compiled_for[c];
+            return forced;
+        }
+    const int order[4] = {1, 2, 3, 0};             // 16 rows a thread first: measured best wherever its block fits 512 threads
     for (int pass = 0; pass < 2; ++pass)
-        for (int c = 0; c < 4; ++c) {
+        for (int o = 0; o < 4; ++o) {
+            const int c = order[o];
             const int dg = (D + cands[c] - 1) / cands[c];
             if (static_cast<long long>(V) * dg <= limits[pass][c]) {
                 *dg_out = dg;
@@ -295,7 +350,10 @@ extern "C" int llm_gla_scan(
     int DG = 0, MT = 0;
     const int R = gla_rows_per_thread(D, V, &DG, &MT);
     if (R == 0) return LLM_REFUSED_SIZE;
-    const size_t smem = static_cast<size_t>(GLA_TB) * (3 * D + V + static_cast<size_t>(DG) * V) * sizeof(float);
+    const size_t smem = static_cast<size_t>(GLA_TB) * (2 * (3 * D + V) + static_cast<size_t>(DG) * V) * sizeof(float);
+    // sixteen-byte copies into the staging buffers want every row piece on a sixteen-byte boundary
+    const int vec = D % 4 == 0 && V % 4 == 0 && stride % 4 == 0 && q_off % 4 == 0 && k_off % 4 == 0 && v_off % 4 == 0 &&
+                    aligned16(proj) && aligned16(la);
     if (smem > 220 * 1024) return LLM_REFUSED_SIZE;
     cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
     const dim3 grid(num_items, H), block((V * DG + 31) / 32 * 32);
@@ -309,12 +367,12 @@ extern "C" int llm_gla_scan(
         }                                                                                                         \
         launch_pdl(kern, grid, block, smem, s, proj, stride, q_off, k_off, v_off, g_off, la, norm_w, eps, q_scale, \
                    out_scale, static_cast<TO*>(out), out_stride, out_off, state, entry_slot, entry_q_start,       \
-                   entry_q_len, items, mode, scratch_s, scratch_a, H, D, V, DG);                                  \
+                   entry_q_len, items, mode, scratch_s, scratch_a, H, D, V, DG, vec);                             \
     } while (0)
 #define BY_R(TO)                                                                                                  \
     switch (R) {                                                                                                  \
         case 8: LAUNCH(8, 1024, TO); break;                                                                       \
-        case 16: LAUNCH(16, 768, TO); break;                                                                      \
+        case 16: LAUNCH(16, 1024, TO); break;                                                                     \
         case 32: LAUNCH(32, 512, TO); break;                                                                      \
         default:                                                                                                  \
             if (MT == 384) LAUNCH(64, 384, TO);                                                                   \
@@ -355,7 +413,7 @@ __global__ void gla_step_kernel(
     for (int d = tid; d < D; d += blockDim.x) {
         sq[d] = pr[q_off + h * D + d] * q_scale;
         sk[d] = pr[k_off + h * D + d];
-        sa[d] = expf(la[row * H * D + h * D + d]);
+        sa[d] = la[row * H * D + h * D + d];           // the decay itself
     }
     for (int c = tid; c < V; c += blockDim.x) sv[c] = pr[v_off + h * V + c];
     __syncthreads();

@@ -525,8 +525,9 @@ def gla_supported(d: int, v: int) -> bool:
 
 def gla_decay(proj: torch.Tensor, a_off: int, rank: int, w2t: torch.Tensor, b2: Optional[torch.Tensor],
               tau: float) -> torch.Tensor:
-    """ln(alpha) = ln(sigmoid(proj[:, a_off : a_off + rank] @ w2t + b2)) / tau as float32 [T, channels];
-    `w2t` is the projection's second half transposed, float32 [rank, channels]."""
+    """The decays alpha = sigmoid(proj[:, a_off : a_off + rank] @ w2t + b2) ^ (1 / tau) as float32 [T, channels]
+    (computed as exp(ln(sigmoid(z)) / tau), which neither side of z overflows); `w2t` is the projection's
+    second half transposed, float32 [rank, channels]."""
     _dev(w2t, b2)
     if proj.dtype != torch.float32 or proj.stride(1) != 1 or w2t.dtype != torch.float32 or w2t.shape[0] != rank:
         raise KernelError("gla_decay wants a float32 projection and a float32 w2t [rank, channels]")
@@ -539,14 +540,16 @@ def gla_decay(proj: torch.Tensor, a_off: int, rank: int, w2t: torch.Tensor, b2: 
     return la
 
 
-def gla_scan(proj: torch.Tensor, offs, la: torch.Tensor, norm_w: torch.Tensor, eps: float, q_scale: float,
+def gla_scan(proj: torch.Tensor, offs, alpha: torch.Tensor, norm_w: torch.Tensor, eps: float, q_scale: float,
              out_scale: float, out: torch.Tensor, out_off: int, state: torch.Tensor, entry_slot, entry_q_start,
              entry_q_len, items: Optional[torch.Tensor], num_items: int, mode: int,
              scratch_s: Optional[torch.Tensor], scratch_a: Optional[torch.Tensor], H: int, D: int, V: int) -> None:
     """The recurrence S <- diag(alpha) S + k v^T, o = S^T q over the tokens of each work item, per head, with
     the per-head RMS norm of o (weight `norm_w` [V]), the silu output gate and `out_scale` applied before
     the store into columns out_off .. out_off + H*V of `out`.  `offs` = (q, k, v, g) column offsets in the
-    float32 projection; `state` float32 [slots, H, D, V]; see csrc/linear_attention.cu for the modes."""
+    float32 projection; `alpha` float32 [T, H*D] from `gla_decay`; `state` float32 [slots, H, D, V]; see
+    csrc/linear_attention.cu for the modes."""
+    la = alpha
     _dev(la, norm_w, state, entry_slot, entry_q_start, entry_q_len, items, scratch_s, scratch_a)
     if (proj.dtype != torch.float32 or proj.stride(1) != 1 or la.dtype != torch.float32 or state.dtype != torch.float32
             or tuple(state.shape[1:]) != (H, D, V) or norm_w.dtype != torch.float32 or norm_w.numel() != V
@@ -563,11 +566,12 @@ def gla_scan(proj: torch.Tensor, offs, la: torch.Tensor, norm_w: torch.Tensor, e
              _ptr(scratch_s), _ptr(scratch_a), H, D, V, _stream()), "gla_scan")
 
 
-def gla_step(proj: torch.Tensor, offs, la: torch.Tensor, norm_w: torch.Tensor, eps: float, q_scale: float,
+def gla_step(proj: torch.Tensor, offs, alpha: torch.Tensor, norm_w: torch.Tensor, eps: float, q_scale: float,
              out_scale: float, out: torch.Tensor, out_off: int, state: torch.Tensor, entry_slot, entry_q_start,
              num_entries: int, H: int, D: int, V: int) -> None:
     """`gla_scan` for a step whose entries all bring one token: the state is streamed through once instead
     of being held, which is what a decode step wants (same arguments, same result up to summation order)."""
+    la = alpha
     _dev(la, norm_w, state, entry_slot, entry_q_start)
     if (proj.dtype != torch.float32 or proj.stride(1) != 1 or la.dtype != torch.float32 or state.dtype != torch.float32
             or tuple(state.shape[1:]) != (H, D, V) or norm_w.dtype != torch.float32 or norm_w.numel() != V

@@ -148,9 +148,9 @@ class GatedLinearAttention(BranchMixer):
         b, (H, D, V) = ctx.batch, (self.H, self.D, self.V)
         if ctx.state is None:
             raise RuntimeError("gated linear attention was given no state")
-        la = ops.gla_decay(proj, col0 + self.a_off, self.rank, self.w2, self.b2, self.tau)
+        alpha = ops.gla_decay(proj, col0 + self.a_off, self.rank, self.w2, self.b2, self.tau)
         offs = (col0 + self.q_off, col0 + self.k_off, col0 + self.v_off, col0 + self.g_off)
-        common = (proj, offs, la, self.norm_w, self.eps, D ** -0.5, out_scale, out, out_col0, ctx.state, b.entry_slot,
+        common = (proj, offs, alpha, self.norm_w, self.eps, D ** -0.5, out_scale, out, out_col0, ctx.state, b.entry_slot,
                   b.entry_q_start, b.entry_q_len)
         work = b.preludes.get(ScanWork.name)
         if b.max_q_len == 1:                                 # a decode step: the states stream through once
