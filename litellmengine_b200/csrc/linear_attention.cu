@@ -398,7 +398,8 @@ __global__ void gla_step_kernel(
     const float* __restrict__ proj, long long stride, int q_off, int k_off, int v_off, int g_off,
     const float* __restrict__ la, const float* __restrict__ norm_w, float eps, float q_scale, float out_scale,
     TO* __restrict__ out, long long out_stride, int out_off, float* __restrict__ state,
-    const int32_t* __restrict__ entry_slot, const int32_t* __restrict__ entry_q_start, int H, int D, int V, int DG) {
+    const int32_t* __restrict__ entry_slot, const int32_t* __restrict__ entry_q_start, int H, int D, int V, int DG,
+    int a_off, int rank, const float* __restrict__ w2t, const float* __restrict__ b2, float inv_tau) {
     pdl_begin();
     extern __shared__ __align__(16) float smem[];
     float* sq = smem;                 // [D]
@@ -407,13 +408,34 @@ __global__ void gla_step_kernel(
     float* sv = sa + D;               // [V]
     float* part = sv + V;             // [DG][V]
     float* red = part + DG * V;       // 33
+    float* a1 = red + 33;             // [rank]: the decay projection's first half, when the decays are made here
     const int entry = blockIdx.x, h = blockIdx.y, tid = threadIdx.x;
     const size_t row = static_cast<size_t>(entry_q_start[entry]);
     const float* pr = proj + row * stride;
+    if (!la) {
+        for (int j = tid; j < rank; j += blockDim.x) a1[j] = pr[a_off + j];
+        __syncthreads();
+    }
     for (int d = tid; d < D; d += blockDim.x) {
         sq[d] = pr[q_off + h * D + d] * q_scale;
         sk[d] = pr[k_off + h * D + d];
-        sa[d] = la[row * H * D + h * D + d];           // the decay itself
+        if (la) {
+            sa[d] = la[row * H * D + h * D + d];       // the decay itself
+        } else {                                       // alpha = sigmoid(w2[c, :] . a1 + b2[c]) ^ (1 / tau), as gla_decay_kernel
+            const int c = h * D + d, C = H * D;
+            float z = b2 ? b2[c] : 0.0f;
+            int j = 0;
+            for (; j + 16 <= rank; j += 16) {
+                float w[16];
+#pragma unroll
+                for (int u = 0; u < 16; ++u) w[u] = w2t[static_cast<size_t>(j + u) * C + c];
+#pragma unroll
+                for (int u = 0; u < 16; ++u) z += w[u] * a1[j + u];
+            }
+            for (; j < rank; ++j) z += w2t[static_cast<size_t>(j) * C + c] * a1[j];
+            const float ls = z < 0.0f ? z - log1pf(expf(z)) : -log1pf(expf(-z));
+            sa[d] = expf(ls * inv_tau);
+        }
     }
     for (int c = tid; c < V; c += blockDim.x) sv[c] = pr[v_off + h * V + c];
     __syncthreads();
@@ -464,25 +486,30 @@ extern "C" int llm_gla_step(
     const float* proj, long long stride, int q_off, int k_off, int v_off, int g_off, const float* la,
     const float* norm_w, float eps, float q_scale, float out_scale, void* out, int out_dtype, long long out_stride,
     int out_off, float* state, const int32_t* entry_slot, const int32_t* entry_q_start, int num_entries, int H, int D,
-    int V, uintptr_t stream) {
+    int V, int a_off, int rank, const float* w2t, const float* b2, float tau, uintptr_t stream) {
+    // la null: the decays are computed here from the projection's columns a_off .. a_off + rank (w2t, b2, tau as
+    // for llm_gla_decay), which saves a decode step one launch a layer
     if (num_entries <= 0) return LLM_OK;
     if (H <= 0 || D <= 0 || V <= 0 || H > 65535 || V > 1024) return LLM_REFUSED_SIZE;
+    if (!la && (!w2t || rank <= 0 || rank > 4096 || !(tau > 0.0f))) return LLM_REFUSED_SIZE;
+    if (la) rank = 0;
     int DG = 256 / V;
     if (DG < 1) DG = 1;
     if (DG > D) DG = D;
     const int threads = (V * DG + 31) / 32 * 32;
-    const size_t smem = (3 * static_cast<size_t>(D) + V + static_cast<size_t>(DG) * V + 33) * sizeof(float);
+    const size_t smem = (3 * static_cast<size_t>(D) + V + static_cast<size_t>(DG) * V + 33 + rank) * sizeof(float);
     if (smem > 48 * 1024) return LLM_REFUSED_SIZE;
+    const float inv_tau = la ? 0.0f : 1.0f / tau;
     cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
     const dim3 grid(num_entries, H);
     if (out_dtype == LLM_DT_F32)
         launch_pdl((gla_step_kernel<float>), grid, dim3(threads), smem, s, proj, stride, q_off, k_off, v_off, g_off, la, norm_w,
                    eps, q_scale, out_scale, static_cast<float*>(out), out_stride, out_off, state, entry_slot, entry_q_start,
-                   H, D, V, DG);
+                   H, D, V, DG, a_off, rank, w2t, b2, inv_tau);
     else if (out_dtype == LLM_DT_BF16)
         launch_pdl((gla_step_kernel<bf16>), grid, dim3(threads), smem, s, proj, stride, q_off, k_off, v_off, g_off, la, norm_w,
                    eps, q_scale, out_scale, static_cast<bf16*>(out), out_stride, out_off, state, entry_slot, entry_q_start,
-                   H, D, V, DG);
+                   H, D, V, DG, a_off, rank, w2t, b2, inv_tau);
     else
         return LLM_REFUSED_DTYPE;
     return launch_status();

@@ -568,22 +568,29 @@ def gla_scan(proj: torch.Tensor, offs, alpha: torch.Tensor, norm_w: torch.Tensor
 
 def gla_step(proj: torch.Tensor, offs, alpha: torch.Tensor, norm_w: torch.Tensor, eps: float, q_scale: float,
              out_scale: float, out: torch.Tensor, out_off: int, state: torch.Tensor, entry_slot, entry_q_start,
-             num_entries: int, H: int, D: int, V: int) -> None:
+             num_entries: int, H: int, D: int, V: int, decay=None) -> None:
     """`gla_scan` for a step whose entries all bring one token: the state is streamed through once instead
-    of being held, which is what a decode step wants (same arguments, same result up to summation order)."""
+    of being held, which is what a decode step wants (same arguments, same result up to summation order).
+    With `alpha` None the kernel makes the decays itself from `decay` = (a_off, rank, w2t, b2, tau), the
+    arguments of `gla_decay`: one launch fewer."""
     la = alpha
-    _dev(la, norm_w, state, entry_slot, entry_q_start)
-    if (proj.dtype != torch.float32 or proj.stride(1) != 1 or la.dtype != torch.float32 or state.dtype != torch.float32
+    a_off, rank, w2t, b2, tau = decay if decay is not None else (0, 0, None, None, 1.0)
+    if la is None and w2t is None:
+        raise KernelError("gla_step wants the decays or what they are made from")
+    _dev(la, norm_w, state, entry_slot, entry_q_start, w2t, b2)
+    if (proj.dtype != torch.float32 or proj.stride(1) != 1 or (la is not None and la.dtype != torch.float32) or state.dtype != torch.float32
             or tuple(state.shape[1:]) != (H, D, V) or norm_w.dtype != torch.float32 or norm_w.numel() != V
             or out.stride(1) != 1):
         raise KernelError("gla_step: float32 projection, decays and state [slots, H, D, V]; norm weight [V]")
     q_off, k_off, v_off, g_off = offs
     f = _fn("linear_attention", "llm_gla_step",
             [c_void_p, c_longlong, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_float, c_float, c_float, c_void_p,
-             c_int, c_longlong, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p])
+             c_int, c_longlong, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p,
+             c_void_p, c_float, c_void_p])
     _check(f(_ptr(proj), proj.stride(0), q_off, k_off, v_off, g_off, _ptr(la), _ptr(norm_w), float(eps),
              float(q_scale), float(out_scale), _ptr(out), _dt(out), out.stride(0), out_off, _ptr(state),
-             _ptr(entry_slot), _ptr(entry_q_start), num_entries, H, D, V, _stream()), "gla_step")
+             _ptr(entry_slot), _ptr(entry_q_start), num_entries, H, D, V, a_off, rank, _ptr(w2t), _ptr(b2), float(tau),
+             _stream()), "gla_step")
 
 
 def gla_chain(state: torch.Tensor, scratch_s: torch.Tensor, scratch_a: torch.Tensor, chains: torch.Tensor,

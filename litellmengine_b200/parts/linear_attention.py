@@ -148,14 +148,17 @@ class GatedLinearAttention(BranchMixer):
         b, (H, D, V) = ctx.batch, (self.H, self.D, self.V)
         if ctx.state is None:
             raise RuntimeError("gated linear attention was given no state")
-        alpha = ops.gla_decay(proj, col0 + self.a_off, self.rank, self.w2, self.b2, self.tau)
         offs = (col0 + self.q_off, col0 + self.k_off, col0 + self.v_off, col0 + self.g_off)
+        if b.max_q_len == 1:
+            # a decode step: the states stream through once, and the kernel makes the decays itself
+            ops.gla_step(proj, offs, None, self.norm_w, self.eps, D ** -0.5, out_scale, out, out_col0, ctx.state,
+                         b.entry_slot, b.entry_q_start, b.num_entries, H, D, V,
+                         decay=(col0 + self.a_off, self.rank, self.w2, self.b2, self.tau))
+            return
+        alpha = ops.gla_decay(proj, col0 + self.a_off, self.rank, self.w2, self.b2, self.tau)
         common = (proj, offs, alpha, self.norm_w, self.eps, D ** -0.5, out_scale, out, out_col0, ctx.state, b.entry_slot,
                   b.entry_q_start, b.entry_q_len)
         work = b.preludes.get(ScanWork.name)
-        if b.max_q_len == 1:                                 # a decode step: the states stream through once
-            ops.gla_step(*common[:-1], b.num_entries, H, D, V)
-            return
         if work is None:                                     # no work lists: every entry in one pass
             ops.gla_scan(*common, None, b.num_entries, ops.GLA_FULL, None, None, H, D, V)
             return

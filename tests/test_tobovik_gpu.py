@@ -294,6 +294,16 @@ def test_decay_is_sigmoid_to_the_power_one_over_tau():
     z = proj[:, 11:].double() @ w2.double().T + b2.double()
     ref = torch.sigmoid(z) ** (1.0 / tau)
     assert torch.isfinite(la).all() and float(la.min()) >= 0.0 and float(la.max()) <= 1.0
+    # the decode kernel makes the same decays itself: with k = 0 and a state of ones, S' = alpha
+    H, D, V = 3, C // 3, 8
+    wide = torch.zeros(T, 11 + rank + 2 * H * D + 2 * H * V)
+    wide[:, :11 + rank] = proj
+    state = torch.ones((T, H, D, V), dtype=torch.float32, device=DEV)
+    o0 = 11 + rank
+    ops.gla_step(wide.to(DEV), (o0, o0 + H * D, o0 + 2 * H * D, o0 + 2 * H * D + H * V), None, torch.ones(V, device=DEV),
+                 1e-5, 1.0, 1.0, torch.empty((T, H * V), device=DEV), 0, state, _i32(list(range(T))), _i32(list(range(T))),
+                 T, H, D, V, decay=(11, rank, w2.t().contiguous().to(DEV), b2.to(DEV), tau))
+    assert (state[:, :, :, 0].reshape(T, C).double().cpu() - ref).abs().max() < 1e-6
     assert (la.double().cpu() - ref).abs().max() < 1e-6
     # far out on the negative side the decay is tiny but its logarithm is still right
     small = ref > 1e-30
