@@ -537,11 +537,11 @@ def tobovik_dict(width, ff, heads, kv, layers):
     mlp = {"kind": "dense", "ff": ff}
     par = {"type": "parallel", "mlp": mlp, "mixer": {
         "left": {"heads": heads, "kv_heads": kv, "dim": DESIGN_HEAD, "vdim": DESIGN_HEAD, "scale": DESIGN_HEAD ** -0.5,
-                 "q_temp": {"coef": 0.3, "every": 128}},
-        "right": {"heads": max(1, heads // 4), "dim": DESIGN_HEAD, "vdim": DESIGN_HEAD, "tau": 16.0, "rank": 64},
-        "left_scale": 0.8, "right_scale": 0.9}}
+                 "q_temp": {"coef": 0.25, "every": 256}},
+        "right": {"heads": max(1, heads // 4), "dim": DESIGN_HEAD, "vdim": DESIGN_HEAD, "tau": 8.0, "rank": 64},
+        "left_scale": 1.0, "right_scale": 0.5}}
     gla = {"type": "gla", "mlp": mlp,
-           "mixer": {"heads": max(1, heads // 2), "dim": DESIGN_HEAD, "vdim": DESIGN_HEAD, "tau": 16.0, "rank": 64}}
+           "mixer": {"heads": max(1, heads // 2), "dim": DESIGN_HEAD, "vdim": DESIGN_HEAD, "tau": 8.0, "rank": 64}}
     return {"architecture": "Tobovik", "vocab": DESIGN_VOCAB, "width": width, "norm": {"eps": 1e-5},
             "layers": [gla if i % 4 == 3 else par for i in range(layers)]}
 
@@ -659,7 +659,7 @@ def design_bench(args, pk) -> int:
     qw, kw = torch.ones(heads * d, device=dev), torch.ones(kv * d, device=dev)
     prep_bytes = T * ((heads + 2 * kv) * d * 4 + (heads + 2 * kv) * d * 2)
     add("attention_prepare (new: bias, projection norm, temperature, page write)",
-        lambda: ops.attention_prepare(proj, 0, heads * d, (heads + kv) * d, (bq, bk, bv), qw, kw, "projection", 1e-5, (0.3, 128),
+        lambda: ops.attention_prepare(proj, 0, heads * d, (heads + kv) * d, (bq, bk, bv), qw, kw, "projection", 1e-5, (0.25, 256),
                                       cache[:, 0], cache[:, 1], pos, ent, slot0, tbl, heads, kv, d, d, PAGE, status, torch.bfloat16),
         nbytes=prep_bytes)
     qkv = proj[:, :(heads + 2 * kv) * d].contiguous()

@@ -55,13 +55,13 @@ TOBO_A_PAGE, TOBO_A_RANK = 4, 6
 
 # B: ungrouped heads, key width == value width, no query temperature, two different parallel layers
 _B_PAR0 = _parallel(_left(3, 3, 32, 32, every=0, scale=0.3), _right(2, 24, 40, 2.0), 0.7, 1.1, 56)
-_B_PAR1 = _parallel(_left(2, 1, 8, 24, coef=0.9, every=7), _right(2, 16, 16, 16.0), 1.0, 1.0, 88)
+_B_PAR1 = _parallel(_left(2, 1, 8, 24, coef=0.9, every=7), _right(2, 16, 16, 12.0), 1.0, 1.0, 88)
 TOBO_B = _config(131, 48, 3e-6, [_B_PAR0, _B_PAR1, _gla(2, 32, 48, 8.0, 64), _shared(_B_PAR0, 0), _shared(_B_PAR1, 1)])
 TOBO_B_PAGE, TOBO_B_RANK = 16, 3
 
 # C: head size 64 with keys and values alike (a bfloat16 run takes the tuned attention kernels), longer sequences
-_C_PAR = _parallel(_left(4, 2, 64, 64, coef=0.2, every=32, scale=0.09), _right(2, 32, 64, 16.0), 0.9, 0.8, 96)
-TOBO_C = _config(211, 64, 1e-5, [_C_PAR, _gla(2, 16, 32, 16.0, 96), _shared(_C_PAR, 0)])
+_C_PAR = _parallel(_left(4, 2, 64, 64, coef=0.2, every=32, scale=0.09), _right(2, 32, 64, 24.0), 0.75, 0.6, 96)
+TOBO_C = _config(211, 64, 1e-5, [_C_PAR, _gla(2, 16, 32, 6.0, 96), _shared(_C_PAR, 0)])
 TOBO_C_PAGE, TOBO_C_RANK = 16, 8
 
 
