@@ -6,10 +6,11 @@ from .specs import (BlockSpec, FeedForwardSpec, MixerSpec, ModelPlan, NormSpec,
                     PositionSpec, StageSpec)
 from .qwen3 import Qwen3Config
 from .tobovik import TobovikConfig
+from .gubidra import GubidraConfig
 
 __all__ = [
     "ConfigError", "config_class_for", "config_from_dict", "load_config",
     "register_architecture", "registered_architectures", "save_config",
     "unregister_architecture", "BlockSpec", "FeedForwardSpec", "MixerSpec", "ModelPlan",
-    "NormSpec", "PositionSpec", "StageSpec", "Qwen3Config", "TobovikConfig",
+    "NormSpec", "PositionSpec", "StageSpec", "Qwen3Config", "TobovikConfig", "GubidraConfig",
 ]

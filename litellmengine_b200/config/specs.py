@@ -24,6 +24,7 @@ class NormSpec:
     kind: str
     eps: float
     weight_name: str = "weight"
+    # kind 'layernorm': (x - mean) * rsqrt(mean((x - mean)^2) + eps) * w, a weight and no bias.
 
 
 @dataclass(frozen=True)
@@ -63,6 +64,15 @@ class MixerSpec:
     taken from the stored tensor).
     kind 'parallel': the mixers in `branches` side by side on the same input, their results added with
     the weights `branch_scales`.
+    `output_gate_scope` 'channel': one gate value per output channel (W_g is [heads * value_dim, hidden]);
+    'head': one per head (W_g is [heads, hidden]).  `distance_bias` = (rows, far): a learned table
+    [rows, heads] is added to the scaled scores, its row chosen by the distance n = i - j between query and
+    key: n itself below rows/2, then logarithmic steps that reach the last row at n = far.
+    kind 'retention': linear attention with one fixed decay per head (`params`: decay, a tuple of one number
+    per head; eps of the per-head output norm), a rotation on q and k (`position`), keys scaled by
+    head_dim^-1/2, a weightless per-head RMS norm of the output and a silu gate.
+    kind 'mlstm': a matrix memory with exponential input and forget gates, a normaliser vector and a
+    running maximum per head (`params`: gate_cap, eps).
     `tensor_names` renames a mixer's tensors: pairs (the mixer's own name for a tensor, its name in the
     model's files, without the mixer's prefix).
     """
@@ -85,11 +95,16 @@ class MixerSpec:
     branches: Tuple["MixerSpec", ...] = ()
     branch_scales: Tuple[float, ...] = ()
     tensor_names: Tuple[Tuple[str, str], ...] = ()
+    output_gate_scope: str = "channel"
+    distance_bias: Optional[Tuple[int, float]] = None
 
 
 @dataclass(frozen=True)
 class FeedForwardSpec:
     """The per-token part of a layer.  kind 'swiglu': down(silu(gate(x)) * up(x)).
+    kind 'moe': routed experts; `intermediate_size` is one expert's, `params`: experts, top, groups
+    (count, keep) or None, route_scale, limit (the experts' clamp), expert_prefix (expert e's tensors are
+    '<expert_prefix><e>.gate' and so on).
     `tensor_names`: pairs (the part's own name for a tensor, its name in the model's files)."""
     kind: str
     intermediate_size: int = 0
@@ -105,7 +120,12 @@ class BlockSpec:
     arrangement 'pre_norm': h += mixer(norm1(h)); h += ffn(norm2(h)).
     arrangement 'branch_norm': h += norm1(mixer(h)); h += norm2(ffn(h)): the norms sit on the sublayers'
     outputs, and the sublayers read the stream itself.
+    arrangement 'hyper_pre_norm': the pre-norm layer over `streams` copies of the residual stream (see
+    `connections`).
     `feed_forward` None: a layer that is its mixer only.
+    `connections` = (streams, name of the mixer's connection tensors, name of the feed-forward's): each
+    sublayer has tensors `<name>.in` [streams], `<name>.out` [streams], `<name>.mix` [streams, streams]; its
+    input is sum_s in[s] x_s and afterwards x_t <- sum_s mix[s, t] x_s + out[t] * y for all t at once.
     """
     arrangement: str
     mixer: MixerSpec
@@ -115,6 +135,7 @@ class BlockSpec:
     weight_prefix: str = ""
     mixer_norm_name: str = "input_layernorm"
     feed_forward_norm_name: str = "post_attention_layernorm"
+    connections: Optional[Tuple[int, str, str]] = None
 
 
 @dataclass(frozen=True)
@@ -143,6 +164,9 @@ class ModelPlan:
     final_norm_name: str = "model.norm.weight"
     output_name: str = "lm_head.weight"
     embedding_position: Optional[PositionSpec] = None     # an encoding added to the embeddings themselves
+    embedding_scale: float = 1.0                          # the token's row is multiplied by this (in 32-bit)
+    streams: int = 0                                      # > 0: the layers keep so many copies of the residual stream
+                                                          # (equal at the start, summed before the final norm)
 
     def validate(self) -> None:
         if self.hidden_size <= 0 or self.vocab_size <= 0:
@@ -155,6 +179,9 @@ class ModelPlan:
             if not 0 <= st.block < len(self.blocks):
                 raise ValueError(f"stage {s} names layer {st.block}, but there are {len(self.blocks)} layers")
             mixer = self.blocks[st.block].mixer
+            conn = self.blocks[st.block].connections
+            if (conn[0] if conn else 0) != self.streams:
+                raise ValueError(f"stage {s}: the layer's connections do not fit the model's {self.streams} streams")
             if st.cache_from is not None:
                 if not 0 <= st.cache_from < s:
                     raise ValueError(f"stage {s}: cache_from={st.cache_from} is not an earlier stage")

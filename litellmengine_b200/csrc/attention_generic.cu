@@ -25,7 +25,12 @@
 // [pages, 2, nkv, page, d] tensor are the special case dk == dv).  An optional output gate is applied
 // before the store: out = o * sigmoid(gate[t, gate_off + h*dv + i]) * out_scale, and the output row
 // may be a column range of a wider buffer (`out_stride`, `out_off`), which is how a layer that runs
-// several mixers side by side collects their results for ONE output product.
+// several mixers side by side collects their results for ONE output product.  With `gate_per_head` the
+// gate holds one value per head (gate[t, gate_off + h]) instead of one per output channel.
+//
+// An optional learned bias by distance is added to the scaled score: s_j += dist_bias[min(p - j, len - 1),
+// h], a float32 table [len, heads] indexed by the distance itself (whoever owns the table expands its
+// bucketing into one row per distance up to the distance from which the row no longer changes).
 #include "common.cuh"
 #include <math_constants.h>
 
@@ -40,7 +45,8 @@ __global__ void paged_attention_generic_kernel(
     const int32_t* __restrict__ entry_slot, const int32_t* __restrict__ block_table, int table_stride,
     int num_tokens, int nq, int nkv, int d, int dv, int page_size, int window, float scale, int num_pages,
     const float* __restrict__ gate, long long gate_stride, int gate_off, float out_scale,
-    long long out_stride, int out_off, int vec, int32_t* __restrict__ status) {
+    long long out_stride, int out_off, int vec, int32_t* __restrict__ status,
+    const float* __restrict__ dist_bias, int dist_len, int gate_per_head) {
     pdl_begin();
     extern __shared__ float smem[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -93,6 +99,7 @@ __global__ void paged_attention_generic_kernel(
                     for (int i = 0; i < d; ++i) dot += qs[i] * to_f32(kr[i]);
                 }
                 s = dot;
+                if (dist_bias) s += dist_bias[static_cast<size_t>(min(pos - j, dist_len - 1)) * nq + h];
             }
         }
         const float m_new = fmaxf(m, warp_max(s));
@@ -132,7 +139,8 @@ __global__ void paged_attention_generic_kernel(
         if (mw != -CUDART_INF_F) l_all += merge[w2 * (dv + 2) + dv + 1] * expf(mw - m_all);
     }
     T* orow = out + static_cast<size_t>(t) * out_stride + out_off + static_cast<size_t>(h) * dv;
-    const float* grow = gate ? gate + static_cast<size_t>(t) * gate_stride + gate_off + static_cast<size_t>(h) * dv : nullptr;
+    const float* grow = gate ? gate + static_cast<size_t>(t) * gate_stride + gate_off +
+                                   (gate_per_head ? static_cast<size_t>(h) : static_cast<size_t>(h) * dv) : nullptr;
     const float inv = 1.0f / l_all;
     for (int i = threadIdx.x; i < dv; i += AG_WARPS * 32) {
         float o = 0.0f;
@@ -141,7 +149,7 @@ __global__ void paged_attention_generic_kernel(
             if (mw != -CUDART_INF_F) o += merge[w2 * (dv + 2) + i] * expf(mw - m_all);
         }
         o *= inv;
-        if (grow) o *= 1.0f / (1.0f + expf(-grow[i]));
+        if (grow) o *= 1.0f / (1.0f + expf(-grow[gate_per_head ? 0 : i]));
         orow[i] = from_f32<T>(o * out_scale);
     }
 }
@@ -154,10 +162,11 @@ extern "C" int llm_paged_attention_generic_kv(
     const int32_t* token_entry, const int32_t* entry_slot, const int32_t* block_table, int table_stride,
     int num_tokens, int nq, int nkv, int d, int dv, int page_size, int window, float scale, int num_pages,
     const float* gate, long long gate_stride, int gate_off, float out_scale, long long out_stride, int out_off,
-    int32_t* status, uintptr_t stream) {
+    int32_t* status, const float* dist_bias, int dist_len, int gate_per_head, uintptr_t stream) {
     if (num_tokens <= 0) return LLM_OK;
     if (nq <= 0 || nkv <= 0 || nq % nkv != 0 || d <= 0 || d > AG_MAX_D || dv <= 0 || dv > AG_MAX_D || page_size <= 0)
         return LLM_REFUSED_SIZE;
+    if (dist_bias && dist_len <= 0) return LLM_REFUSED_SIZE;
     const int esz = cache_dtype == LLM_DT_F32 ? 4 : 2;
     const int vec = (d % 8 == 0) && aligned16(keys) && (key_page_stride * esz) % 16 == 0;
     const size_t smem = (static_cast<size_t>(d) + static_cast<size_t>(AG_WARPS) * (dv + 2)) * sizeof(float);
@@ -170,7 +179,8 @@ extern "C" int llm_paged_attention_generic_kv(
         static_cast<const T*>(q), static_cast<T*>(out), static_cast<const TC*>(keys),               \
         static_cast<const TC*>(values), key_page_stride, value_page_stride, positions,             \
         token_entry, entry_slot, block_table, table_stride, num_tokens, nq, nkv, d, dv, page_size, \
-        window, scale, num_pages, gate, gate_stride, gate_off, out_scale, out_stride, out_off, vec, status)
+        window, scale, num_pages, gate, gate_stride, gate_off, out_scale, out_stride, out_off, vec, status, \
+        dist_bias, dist_len, gate_per_head)
     if (dtype == LLM_DT_F32 && cache_dtype == LLM_DT_F32) LAUNCH(float, float);
     else if (dtype == LLM_DT_BF16 && cache_dtype == LLM_DT_BF16) LAUNCH(bf16, bf16);
     else if (dtype == LLM_DT_F32 && cache_dtype == LLM_DT_BF16) LAUNCH(float, bf16);
@@ -196,5 +206,5 @@ extern "C" int llm_paged_attention_generic(
                                           cache_dtype, 2 * half, 2 * half, positions, token_entry, entry_slot,
                                           block_table, table_stride, num_tokens, nq, nkv, d, d, page_size, window,
                                           scale, num_pages, nullptr, 0, 0, 1.0f, static_cast<long long>(nq) * d, 0,
-                                          status, stream);
+                                          status, nullptr, 0, 0, stream);
 }

@@ -32,6 +32,8 @@ FAMILIES: Dict[str, List[str]] = {
     "attention_generic": ["attention_generic.cu"],
     "attention_prepare": ["attention_prepare.cu"],
     "linear_attention": ["linear_attention.cu"],
+    "streams": ["streams.cu"],
+    "moe": ["moe.cu"],
     "attention_decode": ["attention_decode.cu"],
     "attention_prefill": ["attention_prefill.cu"],
     "attention_prefill_tcgen05": ["attention_prefill_tcgen05.cu"],

@@ -12,7 +12,7 @@ template <typename T>
 __global__ void embedding_gather_kernel(const int32_t* __restrict__ ids, const T* __restrict__ table,
                                         float* __restrict__ out, int hidden, int vocab,
                                         int32_t* __restrict__ status, const int32_t* __restrict__ feedback,
-                                        int feedback_len) {
+                                        int feedback_len, float scale) {
     pdl_begin();
     const int t = blockIdx.x;
     int id = ids[t];
@@ -28,16 +28,18 @@ __global__ void embedding_gather_kernel(const int32_t* __restrict__ ids, const T
         for (int h = threadIdx.x * 8; h < hidden; h += blockDim.x * 8) {
             float v[8];
             load8(row + h, v);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) v[i] *= scale;      // a design's embedding scale, applied in 32-bit (1: exact)
             store8(o + h, v);
         }
     } else {
-        for (int h = threadIdx.x; h < hidden; h += blockDim.x) o[h] = to_f32(row[h]);
+        for (int h = threadIdx.x; h < hidden; h += blockDim.x) o[h] = to_f32(row[h]) * scale;
     }
 }
 
 extern "C" int llm_embedding_gather(const int32_t* ids, const void* table, int table_dtype, float* out,
                                     int num_tokens, int hidden, int vocab, int32_t* status,
-                                    const int32_t* feedback, int feedback_len, uintptr_t stream) {
+                                    const int32_t* feedback, int feedback_len, float scale, uintptr_t stream) {
     if (num_tokens <= 0) return LLM_OK;
     if (hidden <= 0 || vocab <= 0) return LLM_REFUSED_SIZE;
     if ((hidden & 7) == 0 && (!aligned16(table) || !aligned16(out))) return LLM_REFUSED_ALIGN;
@@ -45,10 +47,10 @@ extern "C" int llm_embedding_gather(const int32_t* ids, const void* table, int t
     cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
     if (table_dtype == LLM_DT_F32)
         launch_pdl((embedding_gather_kernel<float>), dim3(num_tokens), dim3(threads), 0, s, 
-            ids, static_cast<const float*>(table), out, hidden, vocab, status, feedback, feedback_len);
+            ids, static_cast<const float*>(table), out, hidden, vocab, status, feedback, feedback_len, scale);
     else if (table_dtype == LLM_DT_BF16)
         launch_pdl((embedding_gather_kernel<bf16>), dim3(num_tokens), dim3(threads), 0, s, 
-            ids, static_cast<const bf16*>(table), out, hidden, vocab, status, feedback, feedback_len);
+            ids, static_cast<const bf16*>(table), out, hidden, vocab, status, feedback, feedback_len, scale);
     else
         return LLM_REFUSED_DTYPE;
     return launch_status();

@@ -141,8 +141,9 @@ def _i32(t: Optional[torch.Tensor], what: str) -> None:
 
 # ------------------------------------------------------------------------------------------
 def embedding(ids: torch.Tensor, table: torch.Tensor, status: torch.Tensor,
-              out: Optional[torch.Tensor] = None, feedback: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """float32 [T, H] = table[ids]; an id -1-j takes its token from feedback[j] (int32, on the device)."""
+              out: Optional[torch.Tensor] = None, feedback: Optional[torch.Tensor] = None,
+              scale: float = 1.0) -> torch.Tensor:
+    """float32 [T, H] = table[ids] * scale; an id -1-j takes its token from feedback[j] (int32, on the device)."""
     _dev(ids, table, status, out, feedback)
     _i32(ids, "ids")
     if feedback is not None:
@@ -151,9 +152,9 @@ def embedding(ids: torch.Tensor, table: torch.Tensor, status: torch.Tensor,
     if out is None:
         out = torch.empty((T, H), dtype=torch.float32, device=table.device)
     f = _fn("embedding", "llm_embedding_gather",
-            [c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p])
+            [c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_float, c_void_p])
     _check(f(_ptr(ids), _ptr(table), _dt(table), _ptr(out), T, H, V, _ptr(status), _ptr(feedback),
-             feedback.numel() if feedback is not None else 0, _stream()), "embedding")
+             feedback.numel() if feedback is not None else 0, float(scale), _stream()), "embedding")
     return out
 
 
@@ -489,11 +490,16 @@ def paged_attention_generic_kv(q: torch.Tensor, keys: torch.Tensor, values: torc
                                entry_slot, block_table: torch.Tensor, nq: int, nkv: int, dk: int, dv: int,
                                page_size: int, window: Optional[int], scale: float, status: torch.Tensor,
                                out: torch.Tensor, out_off: int = 0, gate: Optional[torch.Tensor] = None,
-                               gate_off: int = 0, out_scale: float = 1.0) -> torch.Tensor:
+                               gate_off: int = 0, out_scale: float = 1.0, dist_bias: Optional[torch.Tensor] = None,
+                               gate_per_head: bool = False) -> torch.Tensor:
     """Causal attention of every token in q [T, nq*dk] over its request's pages of `keys` [pages, nkv, page,
     dk] and `values` [pages, nkv, page, dv] (views with any page stride), written into columns out_off ..
-    out_off + nq*dv of `out`, times sigmoid(gate[:, gate_off + ...]) (float32, optional) and `out_scale`."""
-    _dev(q, positions, token_entry, entry_slot, block_table, status)
+    out_off + nq*dv of `out`, times sigmoid(gate[:, gate_off + ...]) (float32, optional; one value per output
+    channel, or per head with `gate_per_head`) and `out_scale`.  `dist_bias` (float32 [len, nq]): row min(i - j,
+    len - 1) is added to the scaled scores of query i and key j."""
+    _dev(q, positions, token_entry, entry_slot, block_table, status, dist_bias)
+    if dist_bias is not None and (dist_bias.dtype != torch.float32 or dist_bias.dim() != 2 or dist_bias.shape[1] != nq):
+        raise KernelError("dist_bias must be float32 [distances, heads]")
     T = q.shape[0]
     for c, w in ((keys, dk), (values, dv)):
         if (not c.is_cuda or c.dim() != 4 or tuple(c.shape[1:]) != (nkv, page_size, w)
@@ -506,12 +512,13 @@ def paged_attention_generic_kv(q: torch.Tensor, keys: torch.Tensor, values: torc
     f = _fn("attention_generic", "llm_paged_attention_generic_kv",
             [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_longlong, c_longlong, c_void_p, c_void_p, c_void_p,
              c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_longlong,
-             c_int, c_float, c_longlong, c_int, c_void_p, c_void_p])
+             c_int, c_float, c_longlong, c_int, c_void_p, c_void_p, c_int, c_int, c_void_p])
     _check(f(_ptr(q), _ptr(out), _dt(q), _ptr(keys), _ptr(values), _dt(keys), keys.stride(0), values.stride(0),
              _ptr(positions), _ptr(token_entry), _ptr(entry_slot), _ptr(block_table), block_table.shape[1], T, nq, nkv,
              dk, dv, page_size, int(window) if window else 0, float(scale), keys.shape[0], _ptr(gate),
              gate.stride(0) if gate is not None else 0, gate_off, float(out_scale), out.stride(0), out_off,
-             _ptr(status), _stream()), "paged_attention_generic_kv")
+             _ptr(status), _ptr(dist_bias), dist_bias.shape[0] if dist_bias is not None else 0,
+             1 if gate_per_head else 0, _stream()), "paged_attention_generic_kv")
     return out
 
 
@@ -602,6 +609,201 @@ def gla_chain(state: torch.Tensor, scratch_s: torch.Tensor, scratch_a: torch.Ten
             [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_void_p])
     _check(f(_ptr(state), _ptr(scratch_s), _ptr(scratch_a), _ptr(chains), num_chains, _ptr(entry_slot), H, D, V,
              _stream()), "gla_chain")
+
+
+# ---- recurrences with a decay per (token, head) or per head (retention, matrix memories) -------------
+def rotate_qk(proj: torch.Tensor, q_off: int, k_off: int, heads_q: int, heads_k: int, D: int, dims: int,
+              inv_freq: torch.Tensor, positions: torch.Tensor) -> None:
+    """In place on the float32 projection: pairs (i, i + dims/2) of every head of q (from column q_off) and of k
+    (from k_off) turn by the angle float(position) * inv_freq[i]."""
+    _dev(inv_freq, positions)
+    _i32(positions, "positions")
+    if (proj.dtype != torch.float32 or proj.stride(1) != 1 or inv_freq.dtype != torch.float32
+            or inv_freq.numel() * 2 != dims):
+        raise KernelError("rotate_qk wants a float32 projection and inv_freq float32 [dims/2]")
+    f = _fn("linear_attention", "llm_rotate_qk",
+            [c_void_p, c_longlong, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p])
+    _check(f(_ptr(proj), proj.stride(0), q_off, k_off, heads_q, heads_k, D, dims, _ptr(inv_freq), _ptr(positions),
+             proj.shape[0], _stream()), "rotate_qk")
+
+
+def recur_gates(proj: torch.Tensor, i_off: int, f_off: int, i_bias: torch.Tensor, f_bias: torch.Tensor, cap: float,
+                state: torch.Tensor, m_off: int, head_stride: int, entry_slot, entry_q_start, entry_q_len,
+                num_entries: int, H: int) -> torch.Tensor:
+    """The gates of a matrix memory over the tokens of each entry, in order: float32 [3, T, H] = (keep, put,
+    floor) per (token, head), see csrc/linear_attention.cu; the running maximum in `state` moves on."""
+    _dev(i_bias, f_bias, state, entry_slot, entry_q_start, entry_q_len)
+    if proj.dtype != torch.float32 or proj.stride(1) != 1 or state.dtype != torch.float32:
+        raise KernelError("recur_gates wants a float32 projection and state")
+    T = proj.shape[0]
+    gates = torch.empty((3, T, H), dtype=torch.float32, device=proj.device)
+    f = _fn("linear_attention", "llm_recur_gates",
+            [c_void_p, c_longlong, c_int, c_int, c_void_p, c_void_p, c_float, c_void_p, c_longlong, c_void_p, c_longlong,
+             c_longlong, c_longlong, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p])
+    _check(f(_ptr(proj), proj.stride(0), i_off, f_off, _ptr(i_bias), _ptr(f_bias), float(cap), _ptr(gates), T,
+             _ptr(state), m_off, head_stride, state.stride(0), _ptr(entry_slot), _ptr(entry_q_start),
+             _ptr(entry_q_len), num_entries, H, _stream()), "recur_gates")
+    return gates
+
+
+GATE_KINDS = {None: 0, "sigmoid": 1, "silu": 2}
+
+
+def recur_scan(proj: torch.Tensor, offs, alpha: torch.Tensor, a_tok: int, a_head: int,
+               kscale: Optional[torch.Tensor], nfloor: Optional[torch.Tensor], norm_w: Optional[torch.Tensor],
+               norm_stride: int, gate: Optional[str], eps: float, q_scale: float, out_scale: float, out: torch.Tensor,
+               out_off: int, state: torch.Tensor, head_stride: int, entry_slot, entry_q_start, entry_q_len,
+               items: Optional[torch.Tensor], num_items: int, mode: int, scratch_s: Optional[torch.Tensor],
+               scratch_a: Optional[torch.Tensor], H: int, D: int, V: int) -> None:
+    """`gla_scan` for recurrences whose decay is one number per (token, head): alpha[token * a_tok + head * a_head]
+    (a_tok 0: a constant per head).  `kscale` [T, H]: the input scale e; `nfloor` [T, H]: the state keeps a
+    normaliser n beside S and o is divided by max(|n . q|, floor) + 1e-6.  `norm_w` None: a weightless output
+    norm; else its index is head * norm_stride + channel.  `state` [slots, ...] holds per head S [D, V], then
+    n [D], then what else the mixer keeps, `head_stride` floats a head."""
+    _dev(alpha, kscale, nfloor, norm_w, state, entry_slot, entry_q_start, entry_q_len, items, scratch_s, scratch_a)
+    if proj.dtype != torch.float32 or proj.stride(1) != 1 or alpha.dtype != torch.float32 or state.dtype != torch.float32 \
+            or out.stride(1) != 1:
+        raise KernelError("recur_scan: float32 projection, decays and state")
+    q_off, k_off, v_off, g_off = offs
+    f = _fn("linear_attention", "llm_recur_scan",
+            [c_void_p, c_longlong, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_float, c_float, c_float, c_void_p,
+             c_int, c_longlong, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p,
+             c_void_p, c_int, c_int, c_int, c_int, c_longlong, c_longlong, c_void_p, c_void_p, c_int, c_int, c_longlong,
+             c_longlong, c_void_p])
+    _check(f(_ptr(proj), proj.stride(0), q_off, k_off, v_off, g_off, _ptr(alpha), _ptr(norm_w), float(eps),
+             float(q_scale), float(out_scale), _ptr(out), _dt(out), out.stride(0), out_off, _ptr(state),
+             _ptr(entry_slot), _ptr(entry_q_start), _ptr(entry_q_len), _ptr(items), num_items, mode,
+             _ptr(scratch_s), _ptr(scratch_a), H, D, V, 1, a_tok, a_head, _ptr(kscale), _ptr(nfloor), norm_stride,
+             GATE_KINDS[gate], head_stride, state.stride(0), _stream()), "recur_scan")
+
+
+def recur_step(proj: torch.Tensor, offs, alpha: Optional[torch.Tensor], a_strides, norm_w: Optional[torch.Tensor],
+               norm_stride: int, gate: Optional[str], eps: float, q_scale: float, out_scale: float, out: torch.Tensor,
+               out_off: int, state: torch.Tensor, head_stride: int, entry_slot, entry_q_start, num_entries: int,
+               H: int, D: int, V: int, rotation=None, gates=None) -> None:
+    """`recur_scan` for a step whose entries all bring one token.  `alpha` with `a_strides` = (token, head,
+    channel) strides: the decays as they are.  `rotation` = (inv_freq, dims, positions): q and k are rotated
+    inside the kernel.  `gates` = (i_off, f_off, i_bias, f_bias, cap): a matrix memory's gates are made inside
+    the kernel (alpha None), the state keeps a normaliser and the running maximum after it."""
+    inv_freq, dims, positions = rotation if rotation is not None else (None, 0, None)
+    i_off, f_off, i_bias, f_bias, cap = gates if gates is not None else (0, 0, None, None, 0.0)
+    if alpha is None and gates is None:
+        raise KernelError("recur_step wants the decays or what they are made from")
+    _dev(alpha, norm_w, state, entry_slot, entry_q_start, inv_freq, positions, i_bias, f_bias)
+    if proj.dtype != torch.float32 or proj.stride(1) != 1 or state.dtype != torch.float32 or out.stride(1) != 1:
+        raise KernelError("recur_step: float32 projection and state")
+    a_tok, a_head, a_chan = a_strides if alpha is not None else (0, 0, 0)
+    q_off, k_off, v_off, g_off = offs
+    f = _fn("linear_attention", "llm_recur_step",
+            [c_void_p, c_longlong, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_float, c_float, c_float, c_void_p,
+             c_int, c_longlong, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p,
+             c_void_p, c_float, c_longlong, c_longlong, c_longlong, c_int, c_int, c_longlong, c_longlong, c_void_p,
+             c_int, c_void_p, c_float, c_int, c_int, c_void_p, c_void_p, c_void_p])
+    _check(f(_ptr(proj), proj.stride(0), q_off, k_off, v_off, g_off, _ptr(alpha), _ptr(norm_w), float(eps),
+             float(q_scale), float(out_scale), _ptr(out), _dt(out), out.stride(0), out_off, _ptr(state),
+             _ptr(entry_slot), _ptr(entry_q_start), num_entries, H, D, V, 0, 0, None, None, 1.0, a_tok, a_head, a_chan,
+             norm_stride, GATE_KINDS[gate], head_stride, state.stride(0), _ptr(inv_freq), dims, _ptr(positions),
+             float(cap), i_off, f_off, _ptr(i_bias), _ptr(f_bias), _stream()), "recur_step")
+
+
+def recur_chain(state: torch.Tensor, head_stride: int, scratch_s: torch.Tensor, scratch_a: torch.Tensor,
+                chains: torch.Tensor, num_chains: int, entry_slot, H: int, D: int, V: int, normaliser: bool) -> None:
+    """`gla_chain` over states that may keep a normaliser n [D] after S [D, V]."""
+    _dev(state, scratch_s, scratch_a, chains, entry_slot)
+    f = _fn("linear_attention", "llm_recur_chain",
+            [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_longlong, c_longlong,
+             c_void_p])
+    _check(f(_ptr(state), _ptr(scratch_s), _ptr(scratch_a), _ptr(chains), num_chains, _ptr(entry_slot), H, D, V,
+             1 if normaliser else 0, head_stride, state.stride(0), _stream()), "recur_chain")
+
+
+# ---- several residual streams ----------------------------------------------------------------------------
+def stream_norm(streams: torch.Tensor, y, mix: Optional[torch.Tensor], outw: Optional[torch.Tensor],
+                inw: Optional[torch.Tensor], weight: Optional[torch.Tensor], eps: float, center: bool,
+                out_dtype: Optional[torch.dtype], rows: Optional[torch.Tensor] = None,
+                write_back: bool = True) -> Optional[torch.Tensor]:
+    """streams: float32 [S, T, H] (or [T, H]: one stream).  With y (a sublayer's output that has not been added
+    yet, possibly an `ops.PartialSum`): x_t <- sum_s mix[s, t] x_s + outw[t] * y for all t (mix None: the identity,
+    outw None: ones), written back unless `rows` is given.  Then, with `weight`: the norm (`center`: layer norm,
+    else RMS norm) of u = sum_t inw[t] x_t (inw None: the plain sum) times `weight`, returned in `out_dtype` for
+    all rows or for `rows`."""
+    parts, part_stride = 1, 0
+    if isinstance(y, PartialSum):
+        parts, part_stride = y.parts.shape[0], y.parts.stride(0)
+        y = y.parts[0]
+    _dev(streams, y, mix, outw, inw, weight, rows)
+    _i32(rows, "rows")
+    if streams.dtype != torch.float32:
+        raise KernelError("the residual streams are float32")
+    S = streams.shape[0] if streams.dim() == 3 else 1
+    T, H = streams.shape[-2], streams.shape[-1]
+    for t, n in ((mix, S * S), (outw, S), (inw, S), (weight, H)):
+        if t is not None and (t.dtype != torch.float32 or t.numel() != n):
+            raise KernelError("stream_norm: a coefficient tensor of the wrong size or type")
+    if y is not None and tuple(y.shape) != (T, H):
+        raise KernelError("y must have a stream's shape")
+    n = rows.numel() if rows is not None else T
+    out = torch.empty((n, H), dtype=out_dtype, device=streams.device) if weight is not None else None
+    f = _fn("streams", "llm_stream_norm",
+            [c_void_p, c_longlong, c_int, c_void_p, c_int, c_int, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p,
+             c_float, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_void_p])
+    _check(f(_ptr(streams), T * H, S, _ptr(y), _dt(y) if y is not None else 0, parts, part_stride, _ptr(mix), _ptr(outw),
+             _ptr(inw), _ptr(weight), float(eps), 1 if center else 0, _ptr(out), _dt(out) if out is not None else 0,
+             _ptr(rows), n, H, 1 if (write_back and rows is None and y is not None) else 0, _stream()), "stream_norm")
+    return out
+
+
+def stream_fan(x: torch.Tensor, S: int) -> torch.Tensor:
+    """float32 [S, T, H]: S copies of x [T, H]."""
+    _dev(x)
+    if x.dtype != torch.float32:
+        raise KernelError("the residual streams are float32")
+    out = torch.empty((S,) + tuple(x.shape), dtype=torch.float32, device=x.device)
+    f = _fn("streams", "llm_stream_fan", [c_void_p, c_void_p, c_longlong, c_int, c_void_p])
+    _check(f(_ptr(x), _ptr(out), x.numel(), S, _stream()), "stream_fan")
+    return out
+
+
+# ---- routed experts ----------------------------------------------------------------------------------------
+def moe_route(x: torch.Tensor, w_router: torch.Tensor, top: int, groups, route_scale: float, lists: bool = False):
+    """Per token of x [T, W]: sigmoid scores of `w_router` (float32 [E, W]), the `top` best among the experts of
+    the best groups (`groups` = (count, keep) or None), weights normalised and scaled.  Returns the dense float32
+    weights [T, E] (zero where not chosen) and, with `lists`, ids int32 [T, top] and weights float32 [T, top]."""
+    _dev(x, w_router)
+    T, W = x.shape
+    E = w_router.shape[0]
+    if w_router.dtype != torch.float32 or w_router.shape[1] != W:
+        raise KernelError("the router's matrix must be float32 [experts, hidden]")
+    dense = torch.empty((T, E), dtype=torch.float32, device=x.device)
+    ids = torch.empty((T, top), dtype=torch.int32, device=x.device) if lists else None
+    wts = torch.empty((T, top), dtype=torch.float32, device=x.device) if lists else None
+    count, keep = groups if groups is not None else (0, 0)
+    f = _fn("moe", "llm_moe_route",
+            [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float,
+             c_void_p])
+    _check(f(_ptr(x), _dt(x), _ptr(w_router), _ptr(dense), _ptr(ids), _ptr(wts), T, W, E, top, count, keep,
+             float(route_scale), _stream()), "moe_route")
+    return (dense, ids, wts) if lists else dense
+
+
+def moe_act(gate_up, dense: torch.Tensor, E: int, ff: int, limit: float, alpha: float,
+            out_dtype: torch.dtype) -> torch.Tensor:
+    """act [T, E*ff] = dense[t, e] * g * sigmoid(alpha g) * (u + 1), g = min(gate, limit), u = clamp(up, +-limit),
+    from the float32 product [T, E*2*ff] (per expert: ff gate columns, then ff up columns; may be a `PartialSum`)."""
+    parts, part_stride = 1, 0
+    if isinstance(gate_up, PartialSum):
+        parts, part_stride = gate_up.parts.shape[0], gate_up.parts.stride(0)
+        gate_up = gate_up.parts[0]
+    _dev(gate_up, dense)
+    T = gate_up.shape[0]
+    if gate_up.dtype != torch.float32 or gate_up.shape[1] != 2 * E * ff or tuple(dense.shape) != (T, E):
+        raise KernelError("moe_act wants the float32 product [T, experts * 2 * ff] and the weights [T, experts]")
+    act = torch.empty((T, E * ff), dtype=out_dtype, device=gate_up.device)
+    f = _fn("moe", "llm_moe_act",
+            [c_void_p, c_int, c_longlong, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float, c_float, c_void_p])
+    _check(f(_ptr(gate_up), parts, part_stride, _ptr(dense), _ptr(act), _dt(act), T, E, ff, float(limit), float(alpha),
+             _stream()), "moe_act")
+    return act
 
 
 def fast_attention_supported(d: int, group: int) -> bool:

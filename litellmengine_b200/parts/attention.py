@@ -223,14 +223,17 @@ class GatedAttentionMixer(BranchMixer):
     sigmoid(W_g x) on the concatenated heads before the output projection.  No rotation: a model that
     uses this mixer encodes positions elsewhere.  One product yields [q | k | v | g] per token in
     float32; one kernel adds the biases, normalises, applies the temperature and writes keys and values
-    to their pages; the attention kernel applies the gate as it stores."""
+    to their pages; the attention kernel applies the gate as it stores.  The gate may be one value per head
+    (`output_gate_scope` 'head').  `distance_bias` = (rows, far) adds a learned bias table[bucket(i - j), head]
+    to the scaled score of query i and key j (see `distance_bucket`); the mixer expands the stored table
+    [rows, heads] into one row per distance once, when it is loaded."""
 
     graph_safe = True
     any_division_safe = True
 
     _DEFAULT_NAMES = {"q": "q_proj.weight", "k": "k_proj.weight", "v": "v_proj.weight", "g": "g_proj.weight",
                       "o": "o_proj.weight", "q_bias": "q_proj.bias", "k_bias": "k_proj.bias", "v_bias": "v_proj.bias",
-                      "q_norm": "q_norm.weight", "k_norm": "k_norm.weight"}
+                      "q_norm": "q_norm.weight", "k_norm": "k_norm.weight", "rel": "distance_bias"}
 
     def __init__(self, spec: MixerSpec, hidden_size: int, compute_dtype: torch.dtype, device):
         if spec.num_heads <= 0 or spec.num_kv_heads <= 0 or spec.num_heads % spec.num_kv_heads:
@@ -246,6 +249,10 @@ class GatedAttentionMixer(BranchMixer):
             raise ValueError(f"output_gate {spec.output_gate!r}: 'sigmoid' or None")
         if not spec.has_kv:
             raise ValueError("the gated attention mixer keeps its own keys and values")
+        if spec.output_gate_scope not in ("channel", "head"):
+            raise ValueError(f"output_gate_scope {spec.output_gate_scope!r}: 'channel' or 'head'")
+        if spec.window is not None and spec.window <= 0:
+            raise ValueError("an attention window must be positive")
         self.spec, self.hidden, self.dtype, self.device = spec, hidden_size, compute_dtype, torch.device(device)
         self.nq, self.nkv, self.d = spec.num_heads, spec.num_kv_heads, spec.head_dim
         self.scale = spec.scale if spec.scale is not None else 1.0 / math.sqrt(float(self.d))
@@ -253,12 +260,21 @@ class GatedAttentionMixer(BranchMixer):
         self.q_off, self.k_off = 0, self.nq * self.d
         self.v_off = self.k_off + self.nkv * self.d
         self.g_off = self.v_off + self.nkv * self.dv
-        self.in_width = self.g_off + (self.nq * self.dv if spec.output_gate else 0)
+        self.gate_per_head = spec.output_gate is not None and spec.output_gate_scope == "head"
+        self.gate_width = 0 if not spec.output_gate else (self.nq if self.gate_per_head else self.nq * self.dv)
+        self.in_width = self.g_off + self.gate_width
         self.out_width = self.nq * self.dv
         self.biases = None
         self.q_norm_w = self.k_norm_w = None
-        # the tuned bfloat16 kernels read keys and values of one width from one tensor
+        self.dist_table = None                  # float32 [distances, heads], made from the stored table when loaded
+        if spec.distance_bias is not None:
+            rows, far = spec.distance_bias
+            if rows != -1 and not far > rows // 2 >= 1:
+                raise ValueError("distance_bias: the farthest distance must exceed half the number of rows")
+        # the tuned bfloat16 kernels read keys and values of one width from one tensor, add no bias to the
+        # scores and leave the gate to a kernel that takes one value per channel
         self._tuned = (compute_dtype == torch.bfloat16 and self.dv == self.d and self.device.type == "cuda"
+                       and spec.distance_bias is None and not self.gate_per_head
                        and ops.fast_attention_supported(self.d, self.nq // self.nkv))
 
     def parameters(self) -> Dict[str, ParamSpec]:
@@ -266,7 +282,9 @@ class GatedAttentionMixer(BranchMixer):
         p = {n["q"]: ParamSpec((self.nq * self.d, self.hidden)), n["k"]: ParamSpec((self.nkv * self.d, self.hidden)),
              n["v"]: ParamSpec((self.nkv * self.dv, self.hidden)), n["o"]: ParamSpec((self.hidden, self.nq * self.dv))}
         if s.output_gate:
-            p[n["g"]] = ParamSpec((self.nq * self.dv, self.hidden))
+            p[n["g"]] = ParamSpec((self.gate_width, self.hidden))
+        if s.distance_bias is not None:
+            p[n["rel"]] = ParamSpec((s.distance_bias[0], self.nq), role="scale", init=("normal", 0.5))
         if s.bias:
             for key, size in (("q_bias", self.nq * self.d), ("k_bias", self.nkv * self.d), ("v_bias", self.nkv * self.dv)):
                 p[n[key]] = ParamSpec((size,), role="scale", init=("normal", 0.02))
@@ -286,6 +304,17 @@ class GatedAttentionMixer(BranchMixer):
             self.biases = tuple(t[n[k]].contiguous() for k in ("q_bias", "k_bias", "v_bias"))
         if s.qk_norm is not None:
             self.q_norm_w, self.k_norm_w = t[n["q_norm"]].contiguous(), t[n["k_norm"]].contiguous()
+        if s.distance_bias is not None:
+            rel = t[n["rel"]].float()
+            rows, far = rel.shape[0], float(s.distance_bias[1])
+            if not far > rows // 2 >= 1:
+                raise ValueError("distance_bias: the farthest distance must exceed half the number of rows")
+            # from distance ceil(far) on the row no longer changes; a window never asks beyond its size
+            count = int(math.ceil(far)) + 1
+            if s.window is not None:
+                count = min(count, s.window)
+            index = torch.tensor([distance_bucket(d, rows, far) for d in range(count)], dtype=torch.long, device=rel.device)
+            self.dist_table = rel[index].contiguous()
         ops.prepare_streaming(self.w_in)
         ops.prepare_streaming(self.w_o)
 
@@ -320,7 +349,17 @@ class GatedAttentionMixer(BranchMixer):
         ops.paged_attention_generic_kv(
             q, ctx.cache_keys, ctx.cache_values, b.positions, b.token_entry, b.entry_slot, ctx.block_table, self.nq,
             self.nkv, self.d, self.dv, ctx.page_size, s.window, self.scale, ctx.status, out, out_col0,
-            gate=proj if s.output_gate else None, gate_off=col0 + self.g_off, out_scale=out_scale)
+            gate=proj if s.output_gate else None, gate_off=col0 + self.g_off, out_scale=out_scale,
+            dist_bias=self.dist_table, gate_per_head=self.gate_per_head)
+
+
+def distance_bucket(n: int, rows: int, far: float) -> int:
+    """Row of a distance-bias table for the distance n >= 0 between a query and a key: the first rows // 2
+    distances have a row each; farther ones share rows in logarithmic steps, and from `far` on it is the last."""
+    half = rows // 2
+    if n < half:
+        return n
+    return min(rows - 1, half + int(math.floor(math.log(n / half) / math.log(far / half) * (rows - half))))
 
 
 _slots = {}

@@ -11,6 +11,49 @@ from .context import StageContext
 from .registry import lookup, register_arrangement
 
 
+class StreamConnection:
+    """One sublayer's connection to the S residual streams of a model that keeps several: `inp` [S] weighs the
+    streams into the sublayer's input, and after the sublayer x_t <- sum_s mix[s, t] x_s + out[t] * y for all t
+    at once (`mix` is indexed [from, to])."""
+
+    def __init__(self, streams: int):
+        self.streams = streams
+        self.inp = self.out = self.mix = None
+
+    def parameters(self) -> Dict[str, ParamSpec]:
+        S = self.streams
+        return {"in": ParamSpec((S,), role="scale", init=("one_plus_normal", 0.1)),
+                "out": ParamSpec((S,), role="scale", init=("one_plus_normal", 0.1)),
+                "mix": ParamSpec((S, S), role="scale", init=("normal", 0.5))}
+
+    def load(self, tensors: Dict[str, torch.Tensor]) -> None:
+        self.inp, self.out, self.mix = (tensors[k].contiguous() for k in ("in", "out", "mix"))
+
+
+class PendingUpdate:
+    """A sublayer's output that has not joined the streams yet, with the coefficients it joins them by: the
+    kernel that norms the next sublayer's input applies it on the way."""
+
+    def __init__(self, y, connection: StreamConnection):
+        self.y, self.connection = y, connection
+
+
+def _stream_y(y):
+    from ..csrc import ops
+    return ops.as_tensor(y) if isinstance(y, ops.PartialSum) and y.rounds_to is not None else y
+
+
+def streams_norm(streams: torch.Tensor, pending: Optional[PendingUpdate], inp: Optional[torch.Tensor], norm,
+                 out_dtype: torch.dtype, rows: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Apply the pending update (if any), then `norm` of sum_t inp[t] x_t (inp None: the sum of the streams, what
+    a model's final norm reads) for all rows or for `rows`."""
+    from ..csrc import ops
+    c = pending.connection if pending is not None else None
+    return ops.stream_norm(streams, _stream_y(pending.y) if pending is not None else None,
+                           c.mix if c is not None else None, c.out if c is not None else None, inp, norm.weight,
+                           norm.eps, getattr(norm, "center", False), out_dtype, rows=rows)
+
+
 class Block:
     """Holds one layer's mixer, feed-forward and norms, each chosen by the layer's spec."""
 
@@ -28,12 +71,19 @@ class Block:
         else:
             self.feed_forward_norm = None
         self.arrangement = lookup("arrangement", spec.arrangement)
+        # a model with several residual streams: one connection per sublayer
+        self.connections = None
+        if spec.connections is not None:
+            n = spec.connections[0]
+            self.connections = (StreamConnection(n), StreamConnection(n) if self.feed_forward is not None else None)
 
     def _children(self):
         s = self.spec
         out = [(s.mixer_norm_name, self.mixer_norm), (s.mixer.weight_prefix, self.mixer)]
         if self.feed_forward is not None:
             out += [(s.feed_forward_norm_name, self.feed_forward_norm), (s.feed_forward.weight_prefix, self.feed_forward)]
+        if self.connections is not None:
+            out += [(name, c) for name, c in zip(s.connections[1:], self.connections) if c is not None]
         return out
 
     def parts(self):
@@ -120,3 +170,21 @@ def branch_norm(block: Block, h: torch.Tensor, delta: Optional[torch.Tensor], ct
     if narrow is not None:
         tables["stream_copy"] = (h, x)
     return h, None
+
+
+@register_arrangement("hyper_pre_norm")
+def hyper_pre_norm(block: Block, h: torch.Tensor, delta, ctx: StageContext):
+    """The pre-norm layer over S residual streams (`h`: float32 [S, T, hidden]).  For each sublayer with its
+    `StreamConnection` c: u = sum_s c.inp[s] x_s; y = sublayer(norm(u)); x_t <- sum_s c.mix[s, t] x_s + c.out[t] y.
+    The update is not applied when the sublayer returns: it travels on as a `PendingUpdate` (across layers too)
+    and the kernel that makes the next sublayer's normed input applies it as it reads the streams."""
+    c1, c2 = block.connections
+    x = streams_norm(h, delta, c1.inp, block.mixer_norm, block.dtype)
+    ctx.partials_ok = True                                      # the streams' kernel adds a product's k-splits as it reads
+    ctx.residual = None
+    pending = PendingUpdate(block.mixer.forward(x, ctx), c1)
+    if block.feed_forward is not None:
+        x = streams_norm(h, pending, c2.inp, block.feed_forward_norm, block.dtype)
+        extra = {"partials_ok": True} if getattr(block.feed_forward, "supports_partials", False) else {}
+        pending = PendingUpdate(block.feed_forward.forward(x, **extra), c2)
+    return h, pending

@@ -50,3 +50,61 @@ class SwiGLU:
         if residual is not None and ops.linear_into(act, self.w_down, residual):
             return None                                                               # joined the residual in the product
         return ops.linear(act, self.w_down, out_dtype=torch.float32, partials_ok=partials_ok)
+
+
+@register_feed_forward("moe")
+class RoutedExperts:
+    """A mixture of experts.  Router: scores s = sigmoid(W_r x) in 32-bit; experts form groups of neighbours, a
+    group's score is the sum of its two largest scores, and the `top` largest scores among the experts of the
+    `keep` best groups are chosen; their weights are s / (sum of the chosen s + 1e-20) * route_scale.  Expert:
+    down(g * sigmoid(1.702 g) * (u + 1)) with g = min(gate x, limit), u = clamp(up x, -limit, limit), no biases.
+    The result is the weighted sum of the chosen experts' outputs.
+
+    The experts' [gate; up] matrices are stacked into one and their down matrices stand side by side along the
+    input axis: one product gives every expert's gate and up values, the activation kernel multiplies each
+    expert's activations by the token's weight for it (zero for experts that were not chosen) and ONE down
+    product adds the chosen experts' outputs up."""
+
+    graph_safe = True
+    any_division_safe = True
+    supports_partials = True
+    ACT_ALPHA = 1.702
+
+    def __init__(self, spec: FeedForwardSpec, hidden_size: int, compute_dtype: torch.dtype, device):
+        p = dict(spec.params)
+        self.hidden, self.ff, self.dtype = hidden_size, spec.intermediate_size, compute_dtype
+        self.E, self.top = int(p["experts"]), int(p["top"])
+        self.groups = tuple(p["groups"]) if p.get("groups") else None
+        self.route_scale, self.limit = float(p.get("route_scale", 1.0)), float(p["limit"])
+        self.prefix = p.get("expert_prefix", "e")
+        if self.ff <= 0 or self.E <= 0 or not 0 < self.top <= self.E:
+            raise ValueError("routed experts need a positive size, experts and 0 < top <= experts")
+        if self.groups is not None:
+            count, keep = self.groups
+            if self.E % count or not 0 < keep <= count or keep * (self.E // count) < self.top:
+                raise ValueError("the expert groups do not fit the experts that are chosen")
+        self.w_router = self.w_gate_up = self.w_down = None
+
+    def parameters(self) -> Dict[str, ParamSpec]:
+        out = {"router": ParamSpec((self.E, self.hidden), role="scale", init=("normal", 0.5))}
+        for e in range(self.E):
+            out[f"{self.prefix}{e}.gate"] = ParamSpec((self.ff, self.hidden))
+            out[f"{self.prefix}{e}.up"] = ParamSpec((self.ff, self.hidden))
+            out[f"{self.prefix}{e}.down"] = ParamSpec((self.hidden, self.ff))
+        return out
+
+    def load(self, t: Dict[str, torch.Tensor]) -> None:
+        self.w_router = t["router"].float().contiguous()
+        rows = [t[f"{self.prefix}{e}.{k}"] for e in range(self.E) for k in ("gate", "up")]
+        downs = [t[f"{self.prefix}{e}.down"] for e in range(self.E)]
+        dt = torch.float32 if any(x.dtype == torch.float32 for x in rows + downs) else rows[0].dtype
+        self.w_gate_up = torch.cat([x.to(dt) for x in rows], dim=0).contiguous()          # [E * 2 * ff, hidden]
+        self.w_down = torch.cat([x.to(dt) for x in downs], dim=1).contiguous()             # [hidden, E * ff]
+        ops.prepare_streaming(self.w_gate_up)
+        ops.prepare_streaming(self.w_down)
+
+    def forward(self, x: torch.Tensor, partials_ok: bool = False):
+        dense = ops.moe_route(x, self.w_router, self.top, self.groups, self.route_scale)
+        gate_up = ops.linear(x, self.w_gate_up, out_dtype=torch.float32, partials_ok=True)
+        act = ops.moe_act(gate_up, dense, self.E, self.ff, self.limit, self.ACT_ALPHA, self.dtype)
+        return ops.linear(act, self.w_down, out_dtype=torch.float32, partials_ok=partials_ok)

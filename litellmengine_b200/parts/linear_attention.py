@@ -170,3 +170,205 @@ class GatedLinearAttention(BranchMixer):
             ops.gla_scan(*common, work.chunks, work.num_chunks, ops.GLA_LOCAL, scratch_s, scratch_a, H, D, V)
             ops.gla_chain(ctx.state, scratch_s, scratch_a, work.chains, work.num_chains, b.entry_slot, H, D, V)
             ops.gla_scan(*common, work.chunks, work.num_chunks, ops.GLA_OUT, scratch_s, scratch_a, H, D, V)
+
+
+class _HeadDecayRecurrence(BranchMixer):
+    """What the recurrences with ONE decay number per (token, head) share: a state per head that the
+    recurrence kernels of gated linear attention walk (S [D, V], optionally a normaliser n [D] beside it),
+    the step's `ScanWork` (short entries in one pass, long portions as chunks that run side by side and a
+    chain over them), a kernel of their own for decode steps.  A subclass says what its projection holds
+    (`_pieces`), what the scan reads (`_scan_inputs`) and how a decode step is launched (`_step`)."""
+
+    graph_safe = True
+    any_division_safe = False
+    graph_variant_group = ("scan_work",)
+    normaliser = False
+    gate = "silu"
+
+    def _setup(self, spec: MixerSpec, hidden_size: int, compute_dtype: torch.dtype, device, names, extra_state: int):
+        self.H, self.D, self.V = spec.num_heads, spec.head_dim, spec.value_dim or spec.head_dim
+        if self.H <= 0 or self.D <= 0 or self.V <= 0:
+            raise ValueError("a recurrent mixer needs positive heads, key width and value width")
+        self.spec, self.hidden, self.dtype, self.device = spec, hidden_size, compute_dtype, torch.device(device)
+        self.eps = float(dict(spec.params).get("eps", 1e-6))          # of the per-head output norm
+        self.names = dict(names, **dict(spec.tensor_names))
+        hd, hv = self.H * self.D, self.H * self.V
+        self.q_off, self.k_off, self.v_off, self.g_off = 0, hd, 2 * hd, 2 * hd + hv
+        self.in_width = 2 * hd + 2 * hv
+        self.out_width = hv
+        self.columns = self.V + (1 if self.normaliser else 0)          # of a head's state that the kernels walk
+        self.head_floats = self.D * self.columns + extra_state
+        if self.device.type == "cuda" and not ops.gla_supported(self.D, self.columns):
+            raise ValueError(f"a state of {self.D} x {self.columns} per head is more than the recurrence kernel keeps "
+                             "in one block's registers")
+
+    def cache_need(self):
+        return StateNeed((self.H, self.head_floats), "float32")
+
+    def step_prelude(self):
+        return ScanWork()
+
+    def graph_variant(self, batch, padded: bool):
+        work = batch.preludes.get(ScanWork.name)
+        return (work.num_short, work.num_chunks, work.num_chains) if work is not None else 0
+
+    def _load_in_out(self, t, keys) -> None:
+        n = self.names
+        rows = [t[n[k]] for k in keys]
+        dt = torch.float32 if any(x.dtype == torch.float32 for x in rows) else rows[0].dtype
+        self.w_in = torch.cat([x.to(dt) for x in rows], dim=0).contiguous()
+        self.w_o = t[n["o"]].contiguous()
+        ops.prepare_streaming(self.w_in)
+        ops.prepare_streaming(self.w_o)
+
+    def mix(self, proj, col0, ctx: StageContext, out, out_col0, out_scale):
+        b, (H, D, V) = ctx.batch, (self.H, self.D, self.V)
+        if ctx.state is None:
+            raise RuntimeError("a recurrent mixer was given no state")
+        offs = (col0 + self.q_off, col0 + self.k_off, col0 + self.v_off, col0 + self.g_off)
+        if b.max_q_len == 1:                    # a decode step: the states stream through once
+            self._step(proj, col0, offs, ctx, out, out_col0, out_scale)
+            return
+        alpha, a_tok, a_head, kscale, nfloor = self._scan_inputs(proj, col0, offs, ctx)
+        norm_w, norm_stride = self._norm()
+        scan = lambda items, n, mode, ss, sa: ops.recur_scan(
+            proj, offs, alpha, a_tok, a_head, kscale, nfloor, norm_w, norm_stride, self.gate, self.eps, self.q_scale,
+            out_scale, out, out_col0, ctx.state, self.head_floats, b.entry_slot, b.entry_q_start, b.entry_q_len, items, n,
+            mode, ss, sa, H, D, V)
+        work = b.preludes.get(ScanWork.name)
+        if work is None:                        # no work lists: every entry in one pass
+            scan(None, b.num_entries, ops.GLA_FULL, None, None)
+            return
+        if work.num_short:
+            scan(work.short, work.num_short, ops.GLA_FULL, None, None)
+        if work.num_chunks:
+            scratch_s = torch.empty((work.num_chunks, H, D * self.columns), dtype=torch.float32, device=proj.device)
+            scratch_a = torch.empty((work.num_chunks, H, D), dtype=torch.float32, device=proj.device)
+            scan(work.chunks, work.num_chunks, ops.GLA_LOCAL, scratch_s, scratch_a)
+            ops.recur_chain(ctx.state, self.head_floats, scratch_s, scratch_a, work.chains, work.num_chains, b.entry_slot,
+                            H, D, V, self.normaliser)
+            scan(work.chunks, work.num_chunks, ops.GLA_OUT, scratch_s, scratch_a)
+
+
+@register_mixer("retention")
+class RetentionMixer(_HeadDecayRecurrence):
+    """Linear attention with one FIXED decay per head and no denominator.  Per head a state S [D, V] (32-bit, one
+    per request and stage, zero at admission):
+
+        S_t = decay_h S_(t-1) + k_t v_t^T,        o_t = S_t^T q_t
+
+    with q = W_q x and k = W_k x rotated by the mixer's position part (a half-split rotation of the first
+    rotary_dim entries of each head), k times D^-1/2 (applied to the finished sums o, which are linear in k),
+    v = W_v x.  Each head's o is divided by its root mean square (no weight), multiplied by silu(W_g x), and the
+    concatenated heads go through W_o.  One product yields [q | k | v | g] per token in float32.  Prompt
+    portions: a rotation kernel, then the recurrence kernels; decode steps: one kernel that rotates too."""
+
+    _DEFAULT_NAMES = {"q": "q_proj.weight", "k": "k_proj.weight", "v": "v_proj.weight", "g": "g_proj.weight",
+                      "o": "o_proj.weight"}
+
+    def __init__(self, spec: MixerSpec, hidden_size: int, compute_dtype: torch.dtype, device):
+        self._setup(spec, hidden_size, compute_dtype, device, self._DEFAULT_NAMES, 0)
+        decay = dict(spec.params).get("decay")
+        if decay is None or len(decay) != self.H or any(not 0.0 <= float(x) <= 1.0 for x in decay):
+            raise ValueError("retention needs one decay in [0, 1] per head")
+        self.decay = torch.tensor([float(x) for x in decay], dtype=torch.float32, device=self.device)
+        self.q_scale = self.D ** -0.5
+        self.rot = None
+        if spec.position.kind != "none":
+            from .registry import lookup
+            part = lookup("position", spec.position.kind)(spec.position, self.D, device)
+            if not hasattr(part, "inv_freq") or not hasattr(part, "rotary_dim"):
+                raise ValueError("retention rotates q and k: its position part must be a rotation")
+            self.rot = (part.inv_freq, part.rotary_dim)
+
+    def parameters(self) -> Dict[str, ParamSpec]:
+        n, hd, hv = self.names, self.H * self.D, self.H * self.V
+        return {n["q"]: ParamSpec((hd, self.hidden)), n["k"]: ParamSpec((hd, self.hidden)),
+                n["v"]: ParamSpec((hv, self.hidden)), n["g"]: ParamSpec((hv, self.hidden)),
+                n["o"]: ParamSpec((self.hidden, hv))}
+
+    def load(self, t: Dict[str, torch.Tensor]) -> None:
+        self._load_in_out(t, ("q", "k", "v", "g"))
+
+    def _norm(self):
+        return None, 0
+
+    def _scan_inputs(self, proj, col0, offs, ctx):
+        if self.rot is not None:
+            ops.rotate_qk(proj, offs[0], offs[1], self.H, self.H, self.D, self.rot[1], self.rot[0], ctx.batch.positions)
+        return self.decay, 0, 1, None, None
+
+    def _step(self, proj, col0, offs, ctx, out, out_col0, out_scale):
+        b = ctx.batch
+        rotation = (self.rot[0], self.rot[1], b.positions) if self.rot is not None else None
+        ops.recur_step(proj, offs, self.decay, (0, 1, 0), None, 0, self.gate, self.eps, self.q_scale, out_scale, out,
+                       out_col0, ctx.state, self.head_floats, b.entry_slot, b.entry_q_start, b.num_entries, self.H,
+                       self.D, self.V, rotation=rotation)
+
+
+@register_mixer("mlstm")
+class MatrixMemoryMixer(_HeadDecayRecurrence):
+    """A matrix memory with exponential gating (mLSTM).  Per head S [D, V], a normaliser n [D] and a running
+    maximum m (all 32-bit, zero at admission; m starts at 0):
+
+        i = cap tanh((W_i x + b_i) / cap),  f = logsigmoid(cap tanh((W_f x + b_f) / cap))     (log gates, per head)
+        m' = max(f + m, i),  S' = exp(f + m - m') S + exp(i - m') k v^T,  n' likewise with k alone
+        o = S'^T q / (max(|n' . q|, exp(-m')) + 1e-6)
+
+    with q = W_q x D^-1/2 (applied to the finished sums), k = W_k x, v = W_v x.  Each head's o is divided by its
+    root mean square, the concatenated heads are multiplied by a weight over all heads and by sigmoid(W_g x), then
+    W_o.  One product yields [q | k | v | g | i | f] per token in float32.  Prompt portions: a kernel walks each
+    entry's gates in order (the maxima are a scalar chain) and leaves exp(f + m - m'), exp(i - m'), exp(-m') per
+    (token, head); with those the recurrence is linear and runs in the kernels of gated linear attention, the
+    normaliser as one more column of the state.  Decode steps: one kernel that makes the gates itself."""
+
+    normaliser = True
+    gate = "sigmoid"
+
+    _DEFAULT_NAMES = {"q": "q_proj.weight", "k": "k_proj.weight", "v": "v_proj.weight", "g": "g_proj.weight",
+                      "o": "o_proj.weight", "norm": "o_norm.weight", "i": "i_proj.weight", "i_bias": "i_proj.bias",
+                      "f": "f_proj.weight", "f_bias": "f_proj.bias"}
+
+    def __init__(self, spec: MixerSpec, hidden_size: int, compute_dtype: torch.dtype, device):
+        self._setup(spec, hidden_size, compute_dtype, device, self._DEFAULT_NAMES, 1)     # + the running maximum
+        self.cap = float(dict(spec.params).get("gate_cap", 15.0))
+        if not self.cap > 0:
+            raise ValueError("gate_cap must be positive")
+        self.q_scale = self.D ** -0.5
+        self.i_off = self.in_width
+        self.f_off = self.in_width + self.H
+        self.in_width += 2 * self.H
+        self.m_off = self.D * self.columns
+        self.i_bias = self.f_bias = self.norm_w = None
+
+    def parameters(self) -> Dict[str, ParamSpec]:
+        n, hd, hv = self.names, self.H * self.D, self.H * self.V
+        return {n["q"]: ParamSpec((hd, self.hidden)), n["k"]: ParamSpec((hd, self.hidden)),
+                n["v"]: ParamSpec((hv, self.hidden)), n["g"]: ParamSpec((hv, self.hidden)),
+                n["o"]: ParamSpec((self.hidden, hv)),
+                n["norm"]: ParamSpec((hv,), role="scale", init=("one_plus_normal", 0.01)),
+                n["i"]: ParamSpec((self.H, self.hidden)), n["f"]: ParamSpec((self.H, self.hidden)),
+                n["i_bias"]: ParamSpec((self.H,), role="scale", init=("normal", 0.5)),
+                n["f_bias"]: ParamSpec((self.H,), role="scale", init=("one_plus_normal", 0.5))}
+
+    def load(self, t: Dict[str, torch.Tensor]) -> None:
+        n = self.names
+        self._load_in_out(t, ("q", "k", "v", "g", "i", "f"))
+        self.i_bias, self.f_bias = t[n["i_bias"]].float().contiguous(), t[n["f_bias"]].float().contiguous()
+        self.norm_w = t[n["norm"]].float().contiguous()
+
+    def _norm(self):
+        return self.norm_w, self.V
+
+    def _scan_inputs(self, proj, col0, offs, ctx):
+        b = ctx.batch
+        gates = ops.recur_gates(proj, col0 + self.i_off, col0 + self.f_off, self.i_bias, self.f_bias, self.cap, ctx.state,
+                                self.m_off, self.head_floats, b.entry_slot, b.entry_q_start, b.entry_q_len,
+                                b.num_entries, self.H)
+        return gates[0], self.H, 1, gates[1], gates[2]
+
+    def _step(self, proj, col0, offs, ctx, out, out_col0, out_scale):
+        b = ctx.batch
+        ops.recur_step(proj, offs, None, None, self.norm_w, self.V, self.gate, self.eps, self.q_scale, out_scale, out,
+                       out_col0, ctx.state, self.head_floats, b.entry_slot, b.entry_q_start, b.num_entries, self.H,
+                       self.D, self.V, gates=(col0 + self.i_off, col0 + self.f_off, self.i_bias, self.f_bias, self.cap))

@@ -8,7 +8,7 @@ import torch
 from ..config.specs import ModelPlan
 from ..csrc import ops
 from ..weights.loader import ParamSpec, WeightSource, check_source, fetch_tensor
-from .block import Block
+from .block import Block, streams_norm
 from .context import StageContext
 from .registry import lookup
 
@@ -139,13 +139,19 @@ class Model:
             if self.embedding_position is not None:
                 h = self.embedding_position.embed(batch, self.embedding, self.dtype)
             else:
-                h = ops.embedding(batch.token_ids, self.embedding, batch.status, feedback=getattr(batch, "feedback", None))
+                h = ops.embedding(batch.token_ids, self.embedding, batch.status, feedback=getattr(batch, "feedback", None),
+                                  scale=self.plan.embedding_scale)
+            if self.plan.streams:                      # several residual streams, all equal at the start
+                h = ops.stream_fan(h, self.plan.streams)
             delta = None
             for s, st in enumerate(self.plan.order):
                 block = self.blocks[st.block]
                 h, delta = block.forward(h, delta, self.stage_context(s, batch, cache))
             if batch.num_want == 0:
                 return torch.empty((0, self.plan.vocab_size), dtype=torch.float32, device=self.device)
+            if self.plan.streams:                      # the last pending update, the sum of the streams, the norm
+                hn = streams_norm(h, delta, None, self.final_norm, self.dtype, rows=batch.want_rows)
+                return ops.linear(hn, self.output, out_dtype=torch.float32)
             if not getattr(self.final_norm, "accepts_partials", False):
                 delta = ops.as_tensor(delta)
             hn = self.final_norm.forward(h, self.dtype, delta=delta, rows=batch.want_rows)
