@@ -125,6 +125,8 @@ def pre_norm(block: Block, h: torch.Tensor, delta: Optional[torch.Tensor], ctx: 
     ctx.partials_ok = getattr(block.feed_forward_norm, "accepts_partials", False)
     ctx.residual = h                                            # a part may add its result here itself and return None
     a = block.mixer.forward(x, ctx)
+    if block.feed_forward is None:                              # a layer that is its mixer only: its output is what is pending
+        return h, a
     y = block.feed_forward_norm.forward(h, block.dtype, delta=a, write_sum=a is not None)
     extra = {}
     if getattr(block.feed_forward, "supports_partials", False):

@@ -18,6 +18,32 @@ def identity(x):
     return x
 
 
+def bf16_round(x):
+    """What a 16-bit run mode does to an activation between two kernels."""
+    return x.to(torch.bfloat16).to(x.dtype)
+
+
+def bf16_round_jittered(seed):
+    """The same rounding after a relative nudge of up to half a unit in the last place: another
+    implementation's rounding of the same exact value."""
+    g = torch.Generator().manual_seed(seed)
+
+    def act(x):
+        nudge = (torch.rand(x.shape, generator=g, dtype=torch.float64) - 0.5) * 2.0 ** -8
+        return (x * (1.0 + nudge.to(x.dtype))).to(torch.bfloat16).to(x.dtype)
+    return act
+
+
+def hyper_step(xs, y, inp, out, mix):
+    """One sublayer's update of the streams xs (a list of [T, W]): x_t <- sum_s mix[s, t] x_s + out[t] y."""
+    S = len(xs)
+    return [sum(mix[s, t] * xs[s] for s in range(S)) + out[t] * y for t in range(S)]
+
+
+def hyper_input(xs, inp):
+    return sum(inp[s] * xs[s] for s in range(len(xs)))
+
+
 def layer_norm(x, weight, eps):
     """(x - mean) / sqrt(var + eps) * weight, var = mean of squared deviations, no bias."""
     mu = x.mean(dim=-1, keepdim=True)
@@ -27,10 +53,6 @@ def layer_norm(x, weight, eps):
 
 def rms_unit(x, eps):
     return x * torch.rsqrt(x.pow(2).mean(dim=-1, keepdim=True) + eps)
-
-
-def gelu_tanh(z):
-    return 0.5 * z * (1.0 + torch.tanh(math.sqrt(2.0 / math.pi) * (z + 0.044715 * z ** 3)))
 
 
 def embed(ids, w, scale):
@@ -46,6 +68,27 @@ def distance_bucket(n, rows, far):
     return min(rows - 1, half + int(math.floor(math.log(n / half) / math.log(far / half) * (rows - half))))
 
 
+def attention_core(q, k, v, rel, scale, far, window, first_position=0):
+    """q [T, H, D] against keys k [N, G, D] and values v [N, G, V] whose last T belong to the queries (the
+    first query sits at `first_position` = N - T): scores * scale + rel[bucket(i - j), h], keys j with
+    0 <= i - j < window, softmax.  Returns [T, H, V]."""
+    T, H, _ = q.shape
+    G = k.shape[1]
+    rows = rel.shape[0]
+    row_of = [distance_bucket(n, rows, far) for n in range(first_position + T)]
+    out = torch.zeros(T, H, v.shape[2], dtype=F64)
+    for t in range(T):
+        i = first_position + t
+        lo = 0 if window is None else max(0, i - window + 1)
+        js = list(range(lo, i + 1))
+        bias = rel[[row_of[i - j] for j in js]]                     # [n, H]
+        for h in range(H):
+            g = h // (H // G)
+            p = torch.softmax((k[js, g] @ q[t, h]) * scale + bias[:, h], dim=0)
+            out[t, h] = p @ v[js, g]
+    return out
+
+
 def attention(x, w, pre, m, act=identity):
     """Grouped-query softmax attention: no rotation, a learned bias by distance, a window of the last
     `mask.size` keys, one sigmoid output gate per head."""
@@ -56,35 +99,17 @@ def attention(x, w, pre, m, act=identity):
     k = act(xa @ w[f"{pre}.k"].T).view(T, G, D)
     v = act(xa @ w[f"{pre}.v"].T).view(T, G, V)
     gate = torch.sigmoid(xa @ w[f"{pre}.g"].T)                    # [T, H]
-    rel = w[f"{pre}.rel"].to(F64)                                 # [rows, H]
-    rows = rel.shape[0]
     window = m["mask"]["size"] if m.get("mask") else None
-    out = torch.zeros(T, H, V, dtype=F64)
-    for i in range(T):
-        lo = 0 if window is None else max(0, i - window + 1)
-        js = list(range(lo, i + 1))
-        bias = torch.stack([rel[distance_bucket(i - j, rows, m["bias_max"])] for j in js])     # [n, H]
-        for h in range(H):
-            g = h // (H // G)
-            s = (k[js, g] @ q[i, h]) * m["scale"] + bias[:, h]
-            p = torch.softmax(s, dim=0)
-            out[i, h] = p @ v[js, g]
-    out = out * gate[:, :, None]
+    out = attention_core(q, k, v, w[f"{pre}.rel"].to(F64), m["scale"], m["bias_max"], window) * gate[:, :, None]
     return act(out.reshape(T, H * V)) @ w[f"{pre}.o"].T
 
 
 # ---- mLSTM ----------------------------------------------------------------------------------------
-def mlstm(x, w, pre, m, eps, act=identity, state=None):
-    """Matrix memory with exponential gating and a running maximum that starts at 0.  `state` (S, n, mx)
-    per head continues a sequence; the new state is returned beside the output."""
-    T = x.shape[0]
-    H, D, V, cap = m["heads"], m["dim"], m["vdim"], m["gate_cap"]
-    xa = act(x)
-    q = (xa @ w[f"{pre}.q"].T).view(T, H, D) * D ** -0.5
-    k = (xa @ w[f"{pre}.k"].T).view(T, H, D)
-    v = (xa @ w[f"{pre}.v"].T).view(T, H, V)
-    ig = cap * torch.tanh((xa @ w[f"{pre}.i"].T + w[f"{pre}.i.b"]) / cap)                     # [T, H] log input gate
-    fg = torch.nn.functional.logsigmoid(cap * torch.tanh((xa @ w[f"{pre}.f"].T + w[f"{pre}.f.b"]) / cap))
+def mlstm_core(q, k, v, ig, fg, state=None):
+    """q, k [T, H, D] (q already scaled), v [T, H, V], log gates ig, fg [T, H].  Returns o [T, H, V] (divided by
+    its normaliser, not yet normed) and the state (S, n, mx)."""
+    T, H, D = q.shape
+    V = v.shape[2]
     if state is None:
         state = (torch.zeros(H, D, V, dtype=F64), torch.zeros(H, D, dtype=F64), torch.zeros(H, dtype=F64))
     S, n, mx = (t.clone() for t in state)
@@ -98,8 +123,27 @@ def mlstm(x, w, pre, m, eps, act=identity, state=None):
         num = torch.einsum("hdv,hd->hv", S, q[t])
         den = torch.maximum((n * q[t]).sum(-1).abs(), torch.exp(-mx)) + 1e-6
         o[t] = num / den[:, None]
+    return o, (S, n, mx)
+
+
+def log_gates(zi, zf, cap):
+    """The capped log input gate and log forget gate from their pre-activations."""
+    return cap * torch.tanh(zi / cap), torch.nn.functional.logsigmoid(cap * torch.tanh(zf / cap))
+
+
+def mlstm(x, w, pre, m, eps, act=identity, state=None):
+    """Matrix memory with exponential gating and a running maximum that starts at 0.  `state` (S, n, mx)
+    per head continues a sequence; the new state is returned beside the output."""
+    T = x.shape[0]
+    H, D, V, cap = m["heads"], m["dim"], m["vdim"], m["gate_cap"]
+    xa = act(x)
+    q = (xa @ w[f"{pre}.q"].T).view(T, H, D) * D ** -0.5
+    k = (xa @ w[f"{pre}.k"].T).view(T, H, D)
+    v = (xa @ w[f"{pre}.v"].T).view(T, H, V)
+    ig, fg = log_gates(xa @ w[f"{pre}.i"].T + w[f"{pre}.i.b"], xa @ w[f"{pre}.f"].T + w[f"{pre}.f.b"], cap)
+    o, state = mlstm_core(q, k, v, ig, fg, state)
     o = rms_unit(o, eps).reshape(T, H * V) * w[f"{pre}.norm"] * torch.sigmoid(xa @ w[f"{pre}.g"].T)
-    return act(o) @ w[f"{pre}.o"].T, (S, n, mx)
+    return act(o) @ w[f"{pre}.o"].T, state
 
 
 # ---- retention ------------------------------------------------------------------------------------
@@ -111,6 +155,18 @@ def rotate_half(t, positions, dims, base):
     c, s = torch.cos(a)[:, None, :], torch.sin(a)[:, None, :]
     u, v2 = t[..., :half], t[..., half:dims]
     return torch.cat([u * c - v2 * s, v2 * c + u * s, t[..., dims:]], dim=-1)
+
+
+def retention_core(q, k, v, decay, state=None):
+    """S_t = decay_h S_(t-1) + k_t v_t^T, o_t = S_t^T q_t for q, k [T, H, D], v [T, H, V], decay [H]."""
+    T, H, D = q.shape
+    V = v.shape[2]
+    S = torch.zeros(H, D, V, dtype=F64) if state is None else state.clone()
+    o = torch.zeros(T, H, V, dtype=F64)
+    for t in range(T):
+        S = decay[:, None, None] * S + k[t][:, :, None] * v[t][:, None, :]
+        o[t] = torch.einsum("hdv,hd->hv", S, q[t])
+    return o, S
 
 
 def retention(x, w, pre, m, eps, act=identity, state=None, first_position=0):
@@ -126,12 +182,7 @@ def retention(x, w, pre, m, eps, act=identity, state=None, first_position=0):
         q = rotate_half(q, pos, m["rot"]["dims"], m["rot"]["base"])
         k = rotate_half(k, pos, m["rot"]["dims"], m["rot"]["base"])
     k = k * D ** -0.5
-    decay = torch.tensor(m["decay"], dtype=F64)
-    S = torch.zeros(H, D, V, dtype=F64) if state is None else state.clone()
-    o = torch.zeros(T, H, V, dtype=F64)
-    for t in range(T):
-        S = decay[:, None, None] * S + k[t][:, :, None] * v[t][:, None, :]
-        o[t] = torch.einsum("hdv,hd->hv", S, q[t])
+    o, S = retention_core(q, k, v, torch.tensor(m["decay"], dtype=F64), state)
     g = xa @ w[f"{pre}.g"].T
     o = rms_unit(o, eps).reshape(T, H * V) * (g * torch.sigmoid(g))
     return act(o) @ w[f"{pre}.o"].T, S
@@ -214,9 +265,8 @@ def forward(cfg, w, ids, act=identity, layers_out=None):
                 x = x + fn(layer_norm(x, w[f"{L}.norm{q}"], eps))
                 continue
             a, b, mix = w[f"{L}.hc{q}.in"], w[f"{L}.hc{q}.out"], w[f"{L}.hc{q}.mix"]
-            u = sum(a[s] * xs[s] for s in range(streams))
-            y = fn(layer_norm(u, w[f"{L}.norm{q}"], eps))
-            xs = [sum(mix[s, t] * xs[s] for s in range(streams)) + b[t] * y for t in range(streams)]
+            y = fn(layer_norm(hyper_input(xs, a), w[f"{L}.norm{q}"], eps))
+            xs = hyper_step(xs, y, a, b, mix)
         if layers_out is not None:
             layers_out.append(x.clone() if xs is None else sum(xs))
     if xs is not None:
