@@ -158,3 +158,108 @@ extern "C" int llm_moe_act(const float* gu, int parts, long long part_stride, co
         return LLM_REFUSED_DTYPE;
     return launch_status();
 }
+
+// ---- steps of few tokens: only the chosen experts' weights are read --------------------------------------
+// For a decode step the dense form above would stream every expert's matrices for a handful of tokens.
+// These two kernels walk the (token, chosen expert) pairs instead; a warp makes one output feature at a
+// time as a dot product over 16-byte loads of the weight row against the token's row held in shared
+// memory (32-bit accumulation), so the chosen experts' bytes bound them.
+//   moe_gate_up_sparse_kernel   act[pair, f] = w * g * sigmoid(alpha g) * (u + 1) for pair = (token, k-th choice)
+//   moe_down_sparse_kernel      out[token, n] = sum over the token's choices of W_down[e][n, :] . act[pair, :]
+// Weights: `w_gate_up` [E * 2 * ff, W] (per expert ff gate rows, then ff up rows) and `w_down` [W, E * ff].
+#define MOE_SPARSE_WARPS 8
+#define MOE_SPARSE_FEATURES 32
+
+template <typename TW>
+__device__ __forceinline__ float moe_dot(const TW* __restrict__ w, const float* __restrict__ xs, int n, int lane, bool vec) {
+    float acc = 0.0f;
+    if (vec) {
+        for (int i = lane * 8; i < n; i += 256) {
+            float a[8];
+            load8(w + i, a);
+#pragma unroll
+            for (int u = 0; u < 8; ++u) acc += a[u] * xs[i + u];
+        }
+    } else {
+        for (int i = lane; i < n; i += 32) acc += to_f32(w[i]) * xs[i];
+    }
+    return warp_sum(acc);
+}
+
+template <typename TX, typename TW, typename TO>
+__global__ void moe_gate_up_sparse_kernel(const TX* __restrict__ x, const TW* __restrict__ wgu,
+                                          const int32_t* __restrict__ ids, const float* __restrict__ weights,
+                                          TO* __restrict__ act, int W, int ff, int top, float limit, float alpha, int vec) {
+    pdl_begin();
+    extern __shared__ __align__(16) float xs[];        // [W]
+    const int pair = blockIdx.x, t = pair / top;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int e = ids[pair];
+    const float wt = weights[pair];
+    for (int i = threadIdx.x; i < W; i += blockDim.x) xs[i] = to_f32(x[static_cast<size_t>(t) * W + i]);
+    __syncthreads();
+    const int f0 = blockIdx.y * MOE_SPARSE_FEATURES;
+    for (int f = f0 + warp; f < min(ff, f0 + MOE_SPARSE_FEATURES); f += MOE_SPARSE_WARPS) {
+        float out = 0.0f;
+        if (e >= 0) {
+            const TW* gr = wgu + (static_cast<size_t>(e) * 2 * ff + f) * W;
+            float g = moe_dot(gr, xs, W, lane, vec);
+            float u = moe_dot(gr + static_cast<size_t>(ff) * W, xs, W, lane, vec);
+            g = fminf(g, limit);
+            u = fminf(fmaxf(u, -limit), limit);
+            out = wt * (g / (1.0f + expf(-alpha * g))) * (u + 1.0f);
+        }
+        if (lane == 0) act[static_cast<size_t>(pair) * ff + f] = from_f32<TO>(out);
+    }
+}
+
+template <typename TA, typename TW>
+__global__ void moe_down_sparse_kernel(const TA* __restrict__ act, const TW* __restrict__ wd,
+                                       const int32_t* __restrict__ ids, float* __restrict__ out, int W, int ff, int top,
+                                       int E, int vec) {
+    pdl_begin();
+    extern __shared__ __align__(16) float as[];        // [top * ff]
+    const int t = blockIdx.x;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    for (int i = threadIdx.x; i < top * ff; i += blockDim.x) as[i] = to_f32(act[static_cast<size_t>(t) * top * ff + i]);
+    __syncthreads();
+    const int n0 = blockIdx.y * MOE_SPARSE_FEATURES;
+    for (int n = n0 + warp; n < min(W, n0 + MOE_SPARSE_FEATURES); n += MOE_SPARSE_WARPS) {
+        const TW* row = wd + static_cast<size_t>(n) * E * ff;
+        float acc = 0.0f;
+        for (int k = 0; k < top; ++k) {
+            const int e = ids[t * top + k];
+            if (e >= 0) acc += moe_dot(row + static_cast<size_t>(e) * ff, as + k * ff, ff, lane, vec);
+        }
+        if (lane == 0) out[static_cast<size_t>(t) * W + n] = acc;
+    }
+}
+
+extern "C" int llm_moe_sparse(const void* x, int x_dtype, const void* wgu, const void* wd, int w_dtype, const int32_t* ids,
+                              const float* weights, void* act, float* out, int num_tokens, int W, int ff, int E, int top,
+                              float limit, float alpha, uintptr_t stream) {
+    if (num_tokens <= 0) return LLM_OK;
+    if (W <= 0 || ff <= 0 || E <= 0 || top <= 0 || !(limit > 0.0f)) return LLM_REFUSED_SIZE;
+    const size_t smem_a = static_cast<size_t>(W) * sizeof(float), smem_b = static_cast<size_t>(top) * ff * sizeof(float);
+    if (smem_a > 48 * 1024 || smem_b > 48 * 1024) return LLM_REFUSED_SIZE;
+    if (x_dtype != w_dtype) return LLM_REFUSED_DTYPE;       // the activations between the two kernels take the tokens' dtype
+    const int vec = W % 8 == 0 && ff % 8 == 0 && aligned16(wgu) && aligned16(wd);
+    cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+    const dim3 grid_a(num_tokens * top, (ff + MOE_SPARSE_FEATURES - 1) / MOE_SPARSE_FEATURES);
+    const dim3 grid_b(num_tokens, (W + MOE_SPARSE_FEATURES - 1) / MOE_SPARSE_FEATURES);
+    const dim3 block(MOE_SPARSE_WARPS * 32);
+    if (x_dtype == LLM_DT_F32) {
+        launch_pdl((moe_gate_up_sparse_kernel<float, float, float>), grid_a, block, smem_a, s, static_cast<const float*>(x),
+                   static_cast<const float*>(wgu), ids, weights, static_cast<float*>(act), W, ff, top, limit, alpha, vec);
+        launch_pdl((moe_down_sparse_kernel<float, float>), grid_b, block, smem_b, s, static_cast<const float*>(act),
+                   static_cast<const float*>(wd), ids, out, W, ff, top, E, vec);
+    } else if (x_dtype == LLM_DT_BF16) {
+        launch_pdl((moe_gate_up_sparse_kernel<bf16, bf16, bf16>), grid_a, block, smem_a, s, static_cast<const bf16*>(x),
+                   static_cast<const bf16*>(wgu), ids, weights, static_cast<bf16*>(act), W, ff, top, limit, alpha, vec);
+        launch_pdl((moe_down_sparse_kernel<bf16, bf16>), grid_b, block, smem_b, s, static_cast<const bf16*>(act),
+                   static_cast<const bf16*>(wd), ids, out, W, ff, top, E, vec);
+    } else {
+        return LLM_REFUSED_DTYPE;
+    }
+    return launch_status();
+}

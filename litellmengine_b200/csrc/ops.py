@@ -721,16 +721,19 @@ def recur_chain(state: torch.Tensor, head_stride: int, scratch_s: torch.Tensor, 
 def stream_norm(streams: torch.Tensor, y, mix: Optional[torch.Tensor], outw: Optional[torch.Tensor],
                 inw: Optional[torch.Tensor], weight: Optional[torch.Tensor], eps: float, center: bool,
                 out_dtype: Optional[torch.dtype], rows: Optional[torch.Tensor] = None,
-                write_back: bool = True) -> Optional[torch.Tensor]:
+                write_back: bool = True, fan: bool = False) -> Optional[torch.Tensor]:
     """streams: float32 [S, T, H] (or [T, H]: one stream).  With y (a sublayer's output that has not been added
     yet, possibly an `ops.PartialSum`): x_t <- sum_s mix[s, t] x_s + outw[t] * y for all t (mix None: the identity,
     outw None: ones), written back unless `rows` is given.  Then, with `weight`: the norm (`center`: layer norm,
     else RMS norm) of u = sum_t inw[t] x_t (inw None: the plain sum) times `weight`, returned in `out_dtype` for
-    all rows or for `rows`."""
+    all rows or for `rows`.  `fan`: only streams[0] holds data yet (a model's embedding); every stream is read from
+    there and written to its own place."""
     parts, part_stride = 1, 0
     if isinstance(y, PartialSum):
         parts, part_stride = y.parts.shape[0], y.parts.stride(0)
         y = y.parts[0]
+    if fan and (y is not None or rows is not None):
+        raise KernelError("stream_norm: the first fan-out takes no pending update and no row selection")
     _dev(streams, y, mix, outw, inw, weight, rows)
     _i32(rows, "rows")
     if streams.dtype != torch.float32:
@@ -745,22 +748,11 @@ def stream_norm(streams: torch.Tensor, y, mix: Optional[torch.Tensor], outw: Opt
     n = rows.numel() if rows is not None else T
     out = torch.empty((n, H), dtype=out_dtype, device=streams.device) if weight is not None else None
     f = _fn("streams", "llm_stream_norm",
-            [c_void_p, c_longlong, c_int, c_void_p, c_int, c_int, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p,
+            [c_void_p, c_longlong, c_longlong, c_int, c_void_p, c_int, c_int, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p,
              c_float, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_void_p])
-    _check(f(_ptr(streams), T * H, S, _ptr(y), _dt(y) if y is not None else 0, parts, part_stride, _ptr(mix), _ptr(outw),
+    _check(f(_ptr(streams), T * H, 0 if fan else T * H, S, _ptr(y), _dt(y) if y is not None else 0, parts, part_stride, _ptr(mix), _ptr(outw),
              _ptr(inw), _ptr(weight), float(eps), 1 if center else 0, _ptr(out), _dt(out) if out is not None else 0,
-             _ptr(rows), n, H, 1 if (write_back and rows is None and y is not None) else 0, _stream()), "stream_norm")
-    return out
-
-
-def stream_fan(x: torch.Tensor, S: int) -> torch.Tensor:
-    """float32 [S, T, H]: S copies of x [T, H]."""
-    _dev(x)
-    if x.dtype != torch.float32:
-        raise KernelError("the residual streams are float32")
-    out = torch.empty((S,) + tuple(x.shape), dtype=torch.float32, device=x.device)
-    f = _fn("streams", "llm_stream_fan", [c_void_p, c_void_p, c_longlong, c_int, c_void_p])
-    _check(f(_ptr(x), _ptr(out), x.numel(), S, _stream()), "stream_fan")
+             _ptr(rows), n, H, 1 if (write_back and rows is None and (y is not None or fan)) else 0, _stream()), "stream_norm")
     return out
 
 
@@ -804,6 +796,32 @@ def moe_act(gate_up, dense: torch.Tensor, E: int, ff: int, limit: float, alpha: 
     _check(f(_ptr(gate_up), parts, part_stride, _ptr(dense), _ptr(act), _dt(act), T, E, ff, float(limit), float(alpha),
              _stream()), "moe_act")
     return act
+
+
+def moe_sparse(x: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor,
+               ff: int, limit: float, alpha: float) -> torch.Tensor:
+    """The routed feed-forward for steps of few tokens: only the chosen experts' matrices are read.  x [T, W] and
+    the matrices in one dtype (bfloat16 or float32); `ids`, `weights` [T, top] from `moe_route`.  Returns the
+    float32 sum [T, W] of the chosen experts' weighted outputs."""
+    _dev(x, w_gate_up, w_down, ids, weights)
+    _i32(ids, "ids")
+    T, W = x.shape
+    top = ids.shape[1]
+    E = w_gate_up.shape[0] // (2 * ff)
+    if (w_gate_up.shape != (E * 2 * ff, W) or w_down.shape != (W, E * ff) or w_gate_up.dtype != x.dtype
+            or w_down.dtype != x.dtype or weights.dtype != torch.float32):
+        raise KernelError("moe_sparse: x, [E*2*ff, W] and [W, E*ff] in one dtype, float32 weights [T, top]")
+    act = torch.empty((T * top, ff), dtype=x.dtype, device=x.device)
+    out = torch.empty((T, W), dtype=torch.float32, device=x.device)
+    f = _fn("moe", "llm_moe_sparse",
+            [c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
+             c_int, c_float, c_float, c_void_p])
+    code = f(_ptr(x), _dt(x), _ptr(w_gate_up), _ptr(w_down), _dt(w_down), _ptr(ids), _ptr(weights), _ptr(act), _ptr(out),
+             T, W, ff, E, top, float(limit), float(alpha), _stream())
+    _check(code, "moe_sparse")
+    global launch_count
+    launch_count += 1                      # two kernels in one call
+    return out
 
 
 def fast_attention_supported(d: int, group: int) -> bool:

@@ -12,7 +12,9 @@
 // `mix` is the identity, a null `outw` or `inw` all ones (in = ones: the sum of the streams, which is what
 // the model's final norm reads).  `rows` picks the rows that are read (the final norm runs only where
 // logits are wanted); the new streams are written back only without `rows`.  A null `w`: the streams are
-// updated and nothing is normalised.
+// updated and nothing is normalised.  `read_stride` is the distance between the streams as they are READ: 0 at a
+// model's first layer, where all streams equal the embedding that sits in stream 0 (they are then written out
+// to their own places, so no kernel has to copy the embedding S times).
 //
 // Layer norm: mean, then the mean of the squared deviations (two passes over the row held in shared
 // memory), eps inside the root.  One block per row.
@@ -21,7 +23,7 @@
 #define ST_MAX 8
 
 template <typename TY, typename TO>
-__global__ void stream_norm_kernel(float* __restrict__ streams, long long stream_stride, int S,
+__global__ void stream_norm_kernel(float* __restrict__ streams, long long stream_stride, long long read_stride, int S,
                                    const TY* __restrict__ y, int y_parts, long long y_part_stride,
                                    const float* __restrict__ mix, const float* __restrict__ outw,
                                    const float* __restrict__ inw, const float* __restrict__ w, float eps, int center,
@@ -46,7 +48,7 @@ __global__ void stream_norm_kernel(float* __restrict__ streams, long long stream
         float x[ST_MAX];
 #pragma unroll
         for (int s = 0; s < ST_MAX; ++s)
-            if (s < S) x[s] = xr[s * stream_stride + h];
+            if (s < S) x[s] = xr[s * read_stride + h];
         float acc = 0.0f;
         if (yr) {
             float yv = 0.0f;
@@ -65,7 +67,10 @@ __global__ void stream_norm_kernel(float* __restrict__ streams, long long stream
         } else {
 #pragma unroll
             for (int t = 0; t < ST_MAX; ++t)
-                if (t < S) acc += coef[S * S + S + t] * x[t];
+                if (t < S) {
+                    acc += coef[S * S + S + t] * x[t];
+                    if (write_back) xr[t * stream_stride + h] = x[t];
+                }
         }
         u[h] = acc;
         sum += acc;
@@ -84,7 +89,7 @@ __global__ void stream_norm_kernel(float* __restrict__ streams, long long stream
     for (int h = threadIdx.x; h < hidden; h += blockDim.x) orow[h] = from_f32<TO>((u[h] - mean) * inv * w[h]);
 }
 
-extern "C" int llm_stream_norm(float* streams, long long stream_stride, int S, const void* y, int y_dtype, int y_parts,
+extern "C" int llm_stream_norm(float* streams, long long stream_stride, long long read_stride, int S, const void* y, int y_dtype, int y_parts,
                                long long y_part_stride, const float* mix, const float* outw, const float* inw,
                                const float* w, float eps, int center, void* out, int out_dtype, const int32_t* rows,
                                int num_rows, int hidden, int write_back, uintptr_t stream) {
@@ -105,7 +110,7 @@ extern "C" int llm_stream_norm(float* streams, long long stream_stride, int S, c
                                                        static_cast<int>(smem));                                     \
             if (e != cudaSuccess) return static_cast<int>(e);                                                       \
         }                                                                                                           \
-        launch_pdl(kern, dim3(num_rows), dim3(threads), smem, s, streams, stream_stride, S,                         \
+        launch_pdl(kern, dim3(num_rows), dim3(threads), smem, s, streams, stream_stride, read_stride, S,                         \
                    static_cast<const TY*>(y), y_parts, y_part_stride, mix, outw, inw, w, eps, center,               \
                    static_cast<TO*>(out), rows, hidden, write_back);                                                \
     } while (0)
@@ -117,24 +122,5 @@ extern "C" int llm_stream_norm(float* streams, long long stream_stride, int S, c
     else if (y_dtype == LLM_DT_BF16 && out_dtype == LLM_DT_BF16) LAUNCH(bf16, bf16);
     else return LLM_REFUSED_DTYPE;
 #undef LAUNCH
-    return launch_status();
-}
-
-// streams[s] = x for every s: the S equal copies a model starts from.  x: float32 [n].
-__global__ void stream_fan_kernel(const float* __restrict__ x, float* __restrict__ streams, long long n, int S) {
-    pdl_begin();
-    const long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
-    if (i >= n) return;
-    const float v = x[i];
-    for (int s = 0; s < S; ++s) streams[s * n + i] = v;
-}
-
-extern "C" int llm_stream_fan(const float* x, float* streams, long long n, int S, uintptr_t stream) {
-    if (n <= 0) return LLM_OK;
-    if (S < 1 || S > ST_MAX) return LLM_REFUSED_SIZE;
-    const long long blocks = (n + 255) / 256;
-    if (blocks > 0x7fffffffLL) return LLM_REFUSED_SIZE;
-    launch_pdl(stream_fan_kernel, dim3(static_cast<unsigned>(blocks)), dim3(256), 0, reinterpret_cast<cudaStream_t>(stream),
-               x, streams, n, S);
     return launch_status();
 }

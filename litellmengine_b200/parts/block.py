@@ -44,14 +44,15 @@ def _stream_y(y):
 
 
 def streams_norm(streams: torch.Tensor, pending: Optional[PendingUpdate], inp: Optional[torch.Tensor], norm,
-                 out_dtype: torch.dtype, rows: Optional[torch.Tensor] = None) -> torch.Tensor:
+                 out_dtype: torch.dtype, rows: Optional[torch.Tensor] = None, fan: bool = False) -> torch.Tensor:
     """Apply the pending update (if any), then `norm` of sum_t inp[t] x_t (inp None: the sum of the streams, what
-    a model's final norm reads) for all rows or for `rows`."""
+    a model's final norm reads) for all rows or for `rows`.  `fan`: the streams are still one (the embedding, in
+    streams[0]) and are written out to their places on the way."""
     from ..csrc import ops
     c = pending.connection if pending is not None else None
     return ops.stream_norm(streams, _stream_y(pending.y) if pending is not None else None,
                            c.mix if c is not None else None, c.out if c is not None else None, inp, norm.weight,
-                           norm.eps, getattr(norm, "center", False), out_dtype, rows=rows)
+                           norm.eps, getattr(norm, "center", False), out_dtype, rows=rows, fan=fan)
 
 
 class Block:
@@ -181,7 +182,8 @@ def hyper_pre_norm(block: Block, h: torch.Tensor, delta, ctx: StageContext):
     The update is not applied when the sublayer returns: it travels on as a `PendingUpdate` (across layers too)
     and the kernel that makes the next sublayer's normed input applies it as it reads the streams."""
     c1, c2 = block.connections
-    x = streams_norm(h, delta, c1.inp, block.mixer_norm, block.dtype)
+    # nothing pending: the model's first layer, whose streams are still the embedding in h[0]
+    x = streams_norm(h, delta, c1.inp, block.mixer_norm, block.dtype, fan=delta is None)
     ctx.partials_ok = True                                      # the streams' kernel adds a product's k-splits as it reads
     ctx.residual = None
     pending = PendingUpdate(block.mixer.forward(x, ctx), c1)

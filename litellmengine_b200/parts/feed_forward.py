@@ -61,9 +61,11 @@ class RoutedExperts:
     The result is the weighted sum of the chosen experts' outputs.
 
     The experts' [gate; up] matrices are stacked into one and their down matrices stand side by side along the
-    input axis: one product gives every expert's gate and up values, the activation kernel multiplies each
-    expert's activations by the token's weight for it (zero for experts that were not chosen) and ONE down
-    product adds the chosen experts' outputs up."""
+    input axis.  Prompt portions: one product gives every expert's gate and up values, the activation kernel
+    multiplies each expert's activations by the token's weight for it (zero for experts that were not chosen) and
+    ONE down product adds the chosen experts' outputs up: tensor-core products over all experts.  Steps whose
+    (token, choice) pairs are fewer than the experts (decode steps of a model with many experts) read only the
+    chosen experts' matrices, in two kernels of their own."""
 
     graph_safe = True
     any_division_safe = True
@@ -104,6 +106,11 @@ class RoutedExperts:
         ops.prepare_streaming(self.w_down)
 
     def forward(self, x: torch.Tensor, partials_ok: bool = False):
+        T = x.shape[0]
+        if (T * self.top < self.E and x.dtype == self.w_gate_up.dtype == self.w_down.dtype and self.hidden <= 12288
+                and self.top * self.ff <= 12288):
+            _, ids, weights = ops.moe_route(x, self.w_router, self.top, self.groups, self.route_scale, lists=True)
+            return ops.moe_sparse(x, self.w_gate_up, self.w_down, ids, weights, self.ff, self.limit, self.ACT_ALPHA)
         dense = ops.moe_route(x, self.w_router, self.top, self.groups, self.route_scale)
         gate_up = ops.linear(x, self.w_gate_up, out_dtype=torch.float32, partials_ok=True)
         act = ops.moe_act(gate_up, dense, self.E, self.ff, self.limit, self.ACT_ALPHA, self.dtype)

@@ -138,11 +138,15 @@ class Model:
         with ops.bound_stream():                       # one stream for the whole pass, looked up once
             if self.embedding_position is not None:
                 h = self.embedding_position.embed(batch, self.embedding, self.dtype)
+            elif self.plan.streams:                    # several residual streams, all equal at the start: the embedding goes
+                # to the first and the first layer's kernel writes the others as it reads
+                h = torch.empty((self.plan.streams, batch.num_tokens, self.plan.hidden_size), dtype=torch.float32,
+                                device=self.device)
+                ops.embedding(batch.token_ids, self.embedding, batch.status, out=h[0],
+                              feedback=getattr(batch, "feedback", None), scale=self.plan.embedding_scale)
             else:
                 h = ops.embedding(batch.token_ids, self.embedding, batch.status, feedback=getattr(batch, "feedback", None),
                                   scale=self.plan.embedding_scale)
-            if self.plan.streams:                      # several residual streams, all equal at the start
-                h = ops.stream_fan(h, self.plan.streams)
             delta = None
             for s, st in enumerate(self.plan.order):
                 block = self.blocks[st.block]

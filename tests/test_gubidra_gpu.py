@@ -245,6 +245,14 @@ def test_streams_update_and_norm(S, center):
     ref = pg.layer_norm(u, wn, eps) if center else pg.rms_unit(u, eps) * wn
     assert (got.double().cpu() - ref).abs().max() < 2e-5
     assert torch.equal(streams2.cpu(), torch.stack(xs).float())
+    # a model's first layer: only stream 0 holds the embedding, the others are written on the way
+    first = torch.full((S, T, H), 7.0, device=DEV)
+    first[0] = f32(xs[0])
+    got = ops.stream_norm(first, None, None, None, f32(inp), f32(wn), eps, center, torch.float32, fan=True)
+    u = xs[0] * inp.sum()
+    ref = pg.layer_norm(u, wn, eps) if center else pg.rms_unit(u, eps) * wn
+    assert (got.double().cpu() - ref).abs().max() < 2e-5
+    assert all(torch.equal(first[s2].cpu(), xs[0].float()) for s2 in range(S))
     if S == 1:      # the plain residual stream: x += y, norm(x)
         x = f32(xs[0])
         got = ops.stream_norm(x, f32(y), None, None, None, f32(wn), eps, center, torch.bfloat16)
@@ -509,6 +517,6 @@ def test_expert_activation_and_routed_sum():
                                                                      ("route_scale", 1.7), ("limit", 1.1), ("expert_prefix", "e")))
     part = RoutedExperts(spec, W, torch.float32, DEV)
     part.load({n[len("l0.mlp."):]: t.float().to(DEV) for n, t in w.items()})
-    for rows in (50, 3):         # a prompt portion, a decode step
+    for rows in (50, 3, 2):      # a prompt portion, decode steps (the last one reads only the chosen experts)
         got = _ops().as_tensor(part.forward(x[:rows].float().to(DEV).contiguous()))
         assert (got.double().cpu() - ref[:rows]).abs().max() < 2e-5
