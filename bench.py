@@ -2,7 +2,7 @@
 """Benchmark of the engine on one B200.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--batch 8] [--layers L]
-                    [--impl ours|reference] [--points LIST | --no-points] [--design tobovik [--sizes LIST]]
+                    [--impl ours|reference] [--points LIST | --no-points] [--design tobovik|gubidra [--sizes LIST]]
 
 Headline (`value`): decode tokens/s of `batch` requests whose context ends at 4,096 tokens, on a
 model with the layer sizes of Qwen3-8B (36 layers unless --layers says fewer; the JSON names both
@@ -20,7 +20,8 @@ the Qwen3-32B shape at batch 16 (each sub-record names its sizes).
 `--design tobovik [--sizes w1024,w2048,w4096]` measures something else and prints a line of its own:
 prefill and decode of the Tobovik design beside Qwen3 at equal width, heads, feed-forward, depth and
 vocabulary, and the design's own kernels beside the like kernels of the Qwen3 path with their roofline
-fractions.  Without it the workload and the line above are what they always were.
+fractions.  `--design gubidra` does the same for the Gubidra design beside Tobovik, its closest model.
+Without it the workload and the line above are what they always were.
 
 `--impl reference` times the unmodified reference engine (float32, its only precision) on the same
 shape, batch, context and steps through baseline/reference_arm.py and prints the same keys with
@@ -546,6 +547,183 @@ def tobovik_dict(width, ff, heads, kv, layers):
             "layers": [gla if i % 4 == 3 else par for i in range(layers)]}
 
 
+def gubidra_dict(width, ff, heads, kv, layers):
+    """Retention, retention, attention, matrix memory, and so on; every layer with eight experts of half the
+    feed-forward size of which two are chosen (as many active weights as the dense feed-forward of equal size,
+    four times as many stored); two residual streams; the attention windowed at the decode context."""
+    mlp = {"kind": "moe", "expert": {"ff": ff // 2, "limit": 7.0},
+           "router": {"experts": 8, "top": 2, "scale": 1.0, "groups": {"count": 4, "keep": 2}}}
+    half = max(1, heads // 2)
+    ret = {"type": "retention", "mlp": mlp, "mixer": {
+        "heads": half, "dim": DESIGN_HEAD, "vdim": DESIGN_HEAD, "rot": {"dims": DESIGN_HEAD, "base": 10000.0},
+        "decay": [1.0 - 2.0 ** (-5 - 3 * i / max(1, half - 1)) for i in range(half)]}}
+    att = {"type": "attention", "mlp": mlp, "mixer": {
+        "heads": heads, "kv_heads": kv, "dim": DESIGN_HEAD, "vdim": DESIGN_HEAD, "scale": DESIGN_HEAD ** -0.5,
+        "mask": {"size": 1024}, "bias_max": 2048, "bias_rows": 32}}
+    mem = {"type": "mlstm", "mlp": mlp, "mixer": {"heads": half, "dim": DESIGN_HEAD // 2, "vdim": DESIGN_HEAD, "gate_cap": 15.0}}
+    return {"architecture": "Gubidra", "vocab": DESIGN_VOCAB, "width": width, "norm": {"eps": 1e-5},
+            "embedding": {"scale": 1.0}, "streams": 2, "layers": [(ret, ret, att, mem)[i % 4] for i in range(layers)]}
+
+
+def gubidra_bench(args, pk, measure) -> int:
+    """`--design gubidra`: the design beside Tobovik (the closest model: softmax attention beside a linear
+    recurrence) at equal width, heads, feed-forward, depth and vocabulary, and its kernels beside their like."""
+    import torch
+    from litellmengine_b200.config import config_from_dict
+    from litellmengine_b200.csrc import ops
+    from litellmengine_b200.csrc.microbench import Flusher, timed
+    dev = "cuda:0"
+    sizes = {}
+    for name, (width, ff, heads, kv, layers) in DESIGN_SIZES.items():
+        if args.sizes and name not in args.sizes.split(","):
+            continue
+        sizes[name] = {"shape": {"width": width, "ff": ff, "heads": heads, "kv_heads": kv, "layers": layers, "vocab": DESIGN_VOCAB}}
+        for label, cfg in (("gubidra", gubidra_dict(width, ff, heads, kv, layers)), ("tobovik", tobovik_dict(width, ff, heads, kv, layers))):
+            sizes[name][label] = measure(config_from_dict(cfg))
+            gc.collect()
+            torch.cuda.empty_cache()
+        g, t = sizes[name]["gubidra"], sizes[name]["tobovik"]
+        sizes[name]["gubidra_over_tobovik"] = {k: round(g[k] / t[k], 3) for k in g if k.endswith("tok_s")}
+    flush = Flusher(dev)
+    width, ff, heads, kv, _ = DESIGN_SIZES["w4096"]
+    T, hbm, d = 2048, pk["hbm_gbs"] * 1e9, DESIGN_HEAD
+    kernels = {}
+    props = torch.cuda.get_device_properties(0)
+    fp32_peak = props.multi_processor_count * 128 * 2 * 1.965e9
+
+    def add(name, fn, nbytes=None, flops=None):
+        sec = timed(fn, 5, 3, flush)
+        rec = {"us": round(sec * 1e6, 2)}
+        if nbytes is not None:
+            rec.update(gbs=round(nbytes / sec / 1e9, 1), frac_of_hbm=round(nbytes / sec / hbm, 4))
+        if flops is not None:
+            rec.update(tflops=round(flops / sec / 1e12, 2), frac_of_fp32_peak=round(flops / sec / fp32_peak, 4))
+        kernels[name] = rec
+
+    S = 2
+    streams = torch.randn(S, T, width, device=dev)
+    y = torch.randn(T, width, device=dev)
+    w = torch.ones(width, device=dev)
+    mix, vec = torch.eye(S, device=dev).contiguous(), torch.ones(S, device=dev)
+    add("stream_norm, 2 streams (new: update of the streams + layer norm of their weighted sum)",
+        lambda: ops.stream_norm(streams, y, mix, vec, vec, w, 1e-5, True, torch.bfloat16), nbytes=T * width * (8 * S + 4 + 2))
+    add("stream_norm, 1 stream (new: residual add + layer norm)",
+        lambda: ops.stream_norm(streams[0], y, None, None, None, w, 1e-5, True, torch.bfloat16), nbytes=T * width * (4 + 4 + 4 + 2))
+    add("rmsnorm (like: residual add + norm)", lambda: ops.rmsnorm(streams[0], w, 1e-5, torch.bfloat16, delta=y, write_sum=True),
+        nbytes=T * width * (4 + 4 + 4 + 2))
+    # the recurrences: a 2,048-token portion in chunks of 64, and 64 single tokens
+    H, D, V = heads // 4, d, d
+    gp = torch.randn(T, 2 * H * D + 2 * H * V + 2 * H, device=dev)
+    offs = (0, H * D, 2 * H * D, 2 * H * D + H * V)
+    gout = torch.empty(T, H * V, device=dev, dtype=torch.bfloat16)
+    B = 64
+    slot0 = torch.zeros(1, device=dev, dtype=torch.int32)
+    items = torch.tensor([(0, c, 64, i) for i, c in enumerate(range(0, T, 64))], device=dev, dtype=torch.int32)
+    chains = torch.tensor([(0, 0, T // 64)], device=dev, dtype=torch.int32)
+    q0, qn = torch.zeros(1, device=dev, dtype=torch.int32), torch.full((1,), T, device=dev, dtype=torch.int32)
+    pos = torch.arange(T, device=dev, dtype=torch.int32)
+    decay = torch.full((H,), 0.99, device=dev)
+    invf = torch.pow(torch.tensor(1e4), -torch.arange(0, D, 2, dtype=torch.float32) / D).to(dev)
+    slots = torch.arange(B, device=dev, dtype=torch.int32)
+    dq0 = torch.arange(B, device=dev, dtype=torch.int32)
+    scan_flops = T * H * D * V * 6
+
+    def recurrence(label, head_floats, cols, alpha, a_tok, kscale, nfloor, norm_w, norm_stride, gate, before=None, step=None):
+        state = torch.zeros(B, H, head_floats, device=dev)
+        ss, sa = torch.empty(T // 64, H, D * cols, device=dev), torch.empty(T // 64, H, D, device=dev)
+
+        def chunked():
+            if before is not None:
+                before(state)
+            a = alpha() if callable(alpha) else alpha
+            scan = lambda mode: ops.recur_scan(gp, offs, a[0] if isinstance(a, tuple) else a, a_tok, 1,
+                                               a[1] if isinstance(a, tuple) else kscale, a[2] if isinstance(a, tuple) else nfloor,
+                                               norm_w, norm_stride, gate, 1e-5, D ** -0.5, 1.0, gout, 0, state, head_floats, slot0,
+                                               q0, qn, items, T // 64, mode, ss, sa, H, D, V)
+            scan(ops.GLA_LOCAL)
+            ops.recur_chain(state, head_floats, ss, sa, chains, 1, slot0, H, D, V, cols > V)
+            scan(ops.GLA_OUT)
+        add(f"{label}: one 2048-token portion in chunks of 64 (new)", chunked, flops=scan_flops * cols / V)
+        add(f"{label}: {B} single tokens (new: the decode kernel)", lambda: step(state), nbytes=2 * B * H * D * cols * 4)
+
+    recurrence("retention", D * V, V, decay, 0, None, None, None, 0, "silu",
+               before=lambda st: ops.rotate_qk(gp, offs[0], offs[1], H, H, D, D, invf, pos),
+               step=lambda st: ops.recur_step(gp[:B], offs, decay, (0, 1, 0), None, 0, "silu", 1e-5, D ** -0.5, 1.0, gout[:B], 0, st,
+                                              D * V, slots, dq0, B, H, D, V, rotation=(invf, D, pos[:B])))
+    i_off, f_off = offs[3] + H * V, offs[3] + H * V + H
+    bias = torch.zeros(H, device=dev)
+    nw = torch.ones(H * V, device=dev)
+    hf = D * (V + 1) + 1
+    made = {}
+
+    def gates_of(st):
+        made["g"] = ops.recur_gates(gp, i_off, f_off, bias, bias, 15.0, st, D * (V + 1), hf, slot0, q0, qn, 1, H)
+    recurrence("matrix memory", hf, V + 1, lambda: (made["g"][0], made["g"][1], made["g"][2]), H, None, None, nw, V, "sigmoid",
+               before=gates_of,
+               step=lambda st: ops.recur_step(gp[:B], offs, None, None, nw, V, "sigmoid", 1e-5, D ** -0.5, 1.0, gout[:B], 0, st, hf,
+                                              slots, dq0, B, H, D, V, gates=(i_off, f_off, bias, bias, 15.0)))
+    la = torch.exp(-torch.rand(T, H * D, device=dev) * 0.1)
+    state = torch.zeros(B, H, D, V, device=dev)
+    ss, sa = torch.empty(T // 64, H, D, V, device=dev), torch.empty(T // 64, H, D, device=dev)
+    nv = torch.ones(V, device=dev)
+    args_c = (gp, offs, la, nv, 1e-5, D ** -0.5, 0.9, gout, 0, state, slot0, q0, qn)
+
+    def gla_chunked():
+        ops.gla_scan(*args_c, items, T // 64, ops.GLA_LOCAL, ss, sa, H, D, V)
+        ops.gla_chain(state, ss, sa, chains, 1, slot0, H, D, V)
+        ops.gla_scan(*args_c, items, T // 64, ops.GLA_OUT, ss, sa, H, D, V)
+    add("gla_scan: one 2048-token portion in chunks of 64 (like)", gla_chunked, flops=scan_flops)
+    dqn = torch.ones(B, device=dev, dtype=torch.int32)
+    add(f"gla_step: {B} single tokens (like)",
+        lambda: ops.gla_step(gp[:B], offs, la[:B], nv, 1e-5, D ** -0.5, 0.9, gout[:B], 0, state, slots, dq0, B, H, D, V),
+        nbytes=2 * B * H * D * V * 4)
+    # attention with the distance table and a window, prompt portion and decode, beside the same kernel without them
+    pages = T // PAGE
+    keys = torch.randn(pages, kv, PAGE, d, device=dev).to(torch.bfloat16)
+    vals = torch.randn(pages, kv, PAGE, d, device=dev).to(torch.bfloat16)
+    tbl = torch.arange(pages, device=dev, dtype=torch.int32).view(1, pages)
+    ent = torch.zeros(T, device=dev, dtype=torch.int32)
+    status = torch.zeros(2, dtype=torch.int32, device=dev)
+    qa = torch.randn(T, heads * d, device=dev).to(torch.bfloat16)
+    oa = torch.empty(T, heads * d, device=dev, dtype=torch.bfloat16)
+    gate = torch.randn(T, heads, device=dev)
+    table = torch.randn(1024, heads, device=dev)
+    window = 1024
+    walked = sum(min(p + 1, window) for p in range(T))
+    attn_flops = 4.0 * heads * d * walked
+    for label, kw in (("attention, distance table + head gate (new)", dict(gate=gate, dist_bias=table, gate_per_head=True)),
+                      ("attention, the same kernel without them (like: the framework's general attention kernel)", {})):
+        sec = timed(lambda: ops.paged_attention_generic_kv(qa, keys, vals, pos, ent, slot0, tbl, heads, kv, d, d, PAGE, window, d ** -0.5,
+                                                           status, oa, 0, **kw), 3, 2, flush)
+        kernels[f"{label}: 2048-token portion, window 1024"] = {"us": round(sec * 1e6, 1), "tflops": round(attn_flops / sec / 1e12, 2)}
+    # routed experts: router, activation, and the kernels that read only the chosen experts
+    E, top, fe = 8, 2, ff // 2
+    x = torch.randn(T, width, device=dev).to(torch.bfloat16)
+    wr = torch.randn(E, width, device=dev) * 0.02
+    add("moe_route (new)", lambda: ops.moe_route(x, wr, top, (4, 2), 1.0), nbytes=T * (width * 2 + E * 4))
+    gu = torch.randn(T, 2 * E * fe, device=dev)
+    dense = ops.moe_route(x, wr, top, (4, 2), 1.0)
+    add("moe_act (new: activation of the chosen experts' columns)", lambda: ops.moe_act(gu, dense, E, fe, 7.0, 1.702, torch.bfloat16),
+        nbytes=T * (top * 2 * fe * 4 + E * fe * 2))
+    gub = torch.randn(T, 2 * fe, device=dev).to(torch.bfloat16)
+    add("silu_and_mul (like)", lambda: ops.silu_and_mul(gub), nbytes=T * fe * 6)
+    wgu = (torch.randn(E * 2 * fe, width, device=dev) * 0.02).to(torch.bfloat16)
+    wd = (torch.randn(width, E * fe, device=dev) * 0.02).to(torch.bfloat16)
+    _, ids, wts = ops.moe_route(x[:1], wr, top, (4, 2), 1.0, lists=True)
+    add("moe_sparse, one token (new: two kernels over the chosen experts' matrices)",
+        lambda: ops.moe_sparse(x[:1], wgu, wd, ids, wts, fe, 7.0, 1.702), nbytes=top * 3 * fe * width * 2)
+    wl = (torch.randn(3 * top * fe, width, device=dev) * 0.02).to(torch.bfloat16)
+    add("streaming product of equal bytes, one token (like)", lambda: ops.linear(x[:1], wl, out_dtype=torch.float32),
+        nbytes=top * 3 * fe * width * 2)
+    print(json.dumps({"metric": "tokens/s of the Gubidra design beside Tobovik at equal sizes (bfloat16, random weights)",
+                      "design": "gubidra", "prompt_tokens": 2048, "decode_context": 1024, "steps": args.steps,
+                      "warmup": args.warmup, "sizes": sizes, "kernels_at_w4096": kernels,
+                      "peaks": {"hbm_gbs": pk["hbm_gbs"], "fp32_fma_tflops_nominal": round(fp32_peak / 1e12, 1),
+                                "source": pk["source"]},
+                      "l2": "kernel timings: a 256 MB buffer is overwritten between launches; steps read every weight"}))
+    return 0
+
+
 def design_bench(args, pk) -> int:
     import torch
     from litellmengine_b200.config import config_from_dict
@@ -605,6 +783,8 @@ def design_bench(args, pk) -> int:
         runner.check_status()
         return rec
 
+    if args.design == "gubidra":
+        return gubidra_bench(args, pk, measure)
     sizes = {}
     for name, (width, ff, heads, kv, layers) in DESIGN_SIZES.items():
         if args.sizes and name not in args.sizes.split(","):
@@ -724,8 +904,9 @@ def main() -> int:
     ap.add_argument("--points", default=",".join(ALL_POINTS),
                     help="which extra measurements to take: " + ",".join(ALL_POINTS))
     ap.add_argument("--no-points", action="store_true", help="the headline, prefill and e2e only")
-    ap.add_argument("--design", choices=["tobovik"],
-                    help="instead of the default workload: this design beside Qwen3 at equal sizes, and its kernels")
+    ap.add_argument("--design", choices=["tobovik", "gubidra"],
+                    help="instead of the default workload: this design beside its closest model (tobovik beside Qwen3, "
+                         "gubidra beside tobovik) at equal sizes, and its kernels")
     ap.add_argument("--sizes", default="", help="with --design: which of " + ",".join(DESIGN_SIZES) + " (default: all)")
     args = ap.parse_args()
 

@@ -31,6 +31,8 @@
 // An optional learned bias by distance is added to the scaled score: s_j += dist_bias[min(p - j, len - 1),
 // h], a float32 table [len, heads] indexed by the distance itself (whoever owns the table expands its
 // bucketing into one row per distance up to the distance from which the row no longer changes).
+// With `rows` (int32 [num_tokens]) the kernel works on the listed tokens only (a step's single decoded tokens
+// while its prompt portions take a tensor-core kernel); -1 entries pad the list.
 #include "common.cuh"
 #include <math_constants.h>
 
@@ -46,13 +48,15 @@ __global__ void paged_attention_generic_kernel(
     int num_tokens, int nq, int nkv, int d, int dv, int page_size, int window, float scale, int num_pages,
     const float* __restrict__ gate, long long gate_stride, int gate_off, float out_scale,
     long long out_stride, int out_off, int vec, int32_t* __restrict__ status,
-    const float* __restrict__ dist_bias, int dist_len, int gate_per_head) {
+    const float* __restrict__ dist_bias, int dist_len, int gate_per_head, const int32_t* __restrict__ rows) {
     pdl_begin();
     extern __shared__ float smem[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const long long item = blockIdx.x;
-    const int t = static_cast<int>(item / nq);
-    const int h = static_cast<int>(item - static_cast<long long>(t) * nq);
+    const int listed = static_cast<int>(item / nq);
+    const int h = static_cast<int>(item - static_cast<long long>(listed) * nq);
+    const int t = rows ? rows[listed] : listed;          // `rows`: the tokens to work on (-1: padding of the list)
+    if (t < 0) return;
     const int kvh = h / (nq / nkv);
     float* qs = smem;                                  // [d]
     float* merge = smem + d;                           // [AG_WARPS][dv + 2]: output, maximum, sum of each warp
@@ -162,7 +166,7 @@ extern "C" int llm_paged_attention_generic_kv(
     const int32_t* token_entry, const int32_t* entry_slot, const int32_t* block_table, int table_stride,
     int num_tokens, int nq, int nkv, int d, int dv, int page_size, int window, float scale, int num_pages,
     const float* gate, long long gate_stride, int gate_off, float out_scale, long long out_stride, int out_off,
-    int32_t* status, const float* dist_bias, int dist_len, int gate_per_head, uintptr_t stream) {
+    int32_t* status, const float* dist_bias, int dist_len, int gate_per_head, const int32_t* rows, uintptr_t stream) {
     if (num_tokens <= 0) return LLM_OK;
     if (nq <= 0 || nkv <= 0 || nq % nkv != 0 || d <= 0 || d > AG_MAX_D || dv <= 0 || dv > AG_MAX_D || page_size <= 0)
         return LLM_REFUSED_SIZE;
@@ -180,7 +184,7 @@ extern "C" int llm_paged_attention_generic_kv(
         static_cast<const TC*>(values), key_page_stride, value_page_stride, positions,             \
         token_entry, entry_slot, block_table, table_stride, num_tokens, nq, nkv, d, dv, page_size, \
         window, scale, num_pages, gate, gate_stride, gate_off, out_scale, out_stride, out_off, vec, status, \
-        dist_bias, dist_len, gate_per_head)
+        dist_bias, dist_len, gate_per_head, rows)
     if (dtype == LLM_DT_F32 && cache_dtype == LLM_DT_F32) LAUNCH(float, float);
     else if (dtype == LLM_DT_BF16 && cache_dtype == LLM_DT_BF16) LAUNCH(bf16, bf16);
     else if (dtype == LLM_DT_F32 && cache_dtype == LLM_DT_BF16) LAUNCH(float, bf16);
@@ -206,5 +210,5 @@ extern "C" int llm_paged_attention_generic(
                                           cache_dtype, 2 * half, 2 * half, positions, token_entry, entry_slot,
                                           block_table, table_stride, num_tokens, nq, nkv, d, d, page_size, window,
                                           scale, num_pages, nullptr, 0, 0, 1.0f, static_cast<long long>(nq) * d, 0,
-                                          status, nullptr, 0, 0, stream);
+                                          status, nullptr, 0, 0, nullptr, stream);
 }

@@ -62,7 +62,9 @@ __global__ void __launch_bounds__(AP_THREADS) paged_prefill_attention_kernel(
     const int32_t* __restrict__ entry_slot, const int32_t* __restrict__ entry_q_start,
     const int32_t* __restrict__ entry_q_len, const int32_t* __restrict__ entry_kv_len,
     const int32_t* __restrict__ block_table, int table_stride, int nq, int nkv, int page_size, int window,
-    float scale_log2e, int num_pages, int32_t* __restrict__ status) {
+    float scale_log2e, int num_pages, int32_t* __restrict__ status,
+    const float* __restrict__ dist_bias, int dist_len, const float* __restrict__ head_gate, long long gate_stride,
+    int gate_off, float out_scale, long long out_stride, int out_off) {
     pdl_begin();
     constexpr int CH = D / 8;                     // 16-byte chunks per row
     constexpr int KB = D / 16;                    // k-blocks of the first product
@@ -143,6 +145,8 @@ __global__ void __launch_bounds__(AP_THREADS) paged_prefill_attention_kernel(
     const int lo0 = (window > 0 && pos0 - window + 1 > 0) ? pos0 - window + 1 : 0;
     const int lo1 = (window > 0 && pos1 - window + 1 > 0) ? pos1 - window + 1 : 0;
     const bool live0 = r0 < rows_here, live1 = r0 + 8 < rows_here;
+    // a learned bias by distance, one row of [heads, distances] per head, already in the exp2 domain
+    const float* bias_h = dist_bias ? dist_bias + static_cast<size_t>(h) * dist_len : nullptr;
 
     for (int it = 0; it < n_tiles; ++it) {
         const int kt = k_lo + it * AP_BN, buf = it & 1;
@@ -199,6 +203,10 @@ __global__ void __launch_bounds__(AP_THREADS) paged_prefill_attention_kernel(
             for (int c = 0; c < 2; ++c) {
                 const int key = kt + nb * 8 + (lane & 3) * 2 + c;
                 float a = s[nb][c] * scale_log2e, b2 = s[nb][2 + c] * scale_log2e;
+                if (bias_h) {
+                    a += __ldg(bias_h + min(max(pos0 - key, 0), dist_len - 1));
+                    b2 += __ldg(bias_h + min(max(pos1 - key, 0), dist_len - 1));
+                }
                 if (need_mask) {
                     if (key > pos0 || key < lo0) a = -CUDART_INF_F;
                     if (key > pos1 || key < lo1) b2 = -CUDART_INF_F;
@@ -252,9 +260,13 @@ __global__ void __launch_bounds__(AP_THREADS) paged_prefill_attention_kernel(
     }
     cp_async_wait_all();
 
-    const float inv0 = live0 && l0 > 0.0f ? 1.0f / l0 : 0.0f, inv1 = live1 && l1 > 0.0f ? 1.0f / l1 : 0.0f;
-    bf16* orow0 = out + (static_cast<size_t>(row_base + r0) * nq + h) * D + (lane & 3) * 2;
-    bf16* orow1 = orow0 + static_cast<size_t>(8) * nq * D;
+    float inv0 = live0 && l0 > 0.0f ? out_scale / l0 : 0.0f, inv1 = live1 && l1 > 0.0f ? out_scale / l1 : 0.0f;
+    if (head_gate) {                                  // one sigmoid gate per (token, head)
+        if (live0) inv0 *= 1.0f / (1.0f + expf(-head_gate[static_cast<size_t>(row_base + r0) * gate_stride + gate_off + h]));
+        if (live1) inv1 *= 1.0f / (1.0f + expf(-head_gate[static_cast<size_t>(row_base + r0 + 8) * gate_stride + gate_off + h]));
+    }
+    bf16* orow0 = out + static_cast<size_t>(row_base + r0) * out_stride + out_off + static_cast<size_t>(h) * D + (lane & 3) * 2;
+    bf16* orow1 = orow0 + static_cast<size_t>(8) * out_stride;
 #pragma unroll
     for (int nb = 0; nb < D / 8; ++nb) {
         if (live0) *reinterpret_cast<unsigned*>(orow0 + nb * 8) = pack_bf16(o[nb][0] * inv0, o[nb][1] * inv0);
@@ -266,6 +278,13 @@ extern "C" int llm_paged_prefill_supported(int d) { return d == 64 || d == 128; 
 
 extern "C" int llm_paged_prefill_tile_rows() { return AP_BM; }
 
+extern "C" int llm_paged_attention_prefill_ex(
+    const void* q, void* out, const void* cache, const int32_t* tiles, int n_tiles, const int32_t* entry_slot,
+    const int32_t* entry_q_start, const int32_t* entry_q_len, const int32_t* entry_kv_len,
+    const int32_t* block_table, int table_stride, int nq, int nkv, int d, int page_size, int window, float scale,
+    int num_pages, int32_t* status, const float* dist_bias, int dist_len, const float* head_gate, long long gate_stride,
+    int gate_off, float out_scale, long long out_stride, int out_off, uintptr_t stream);
+
 // q, out: bfloat16 [T, nq*d]; cache: bfloat16 [pages, 2, nkv, page_size, d];
 // tiles: int32 [n_tiles][2] = (entry, first query row of the tile inside the entry), each tile
 // llm_paged_prefill_tile_rows() rows.
@@ -274,9 +293,25 @@ extern "C" int llm_paged_attention_prefill(
     const int32_t* entry_q_start, const int32_t* entry_q_len, const int32_t* entry_kv_len,
     const int32_t* block_table, int table_stride, int nq, int nkv, int d, int page_size, int window, float scale,
     int num_pages, int32_t* status, uintptr_t stream) {
+    return llm_paged_attention_prefill_ex(q, out, cache, tiles, n_tiles, entry_slot, entry_q_start, entry_q_len, entry_kv_len,
+                                          block_table, table_stride, nq, nkv, d, page_size, window, scale, num_pages, status,
+                                          nullptr, 0, nullptr, 0, 0, 1.0f, static_cast<long long>(nq) * d, 0, stream);
+}
+
+// The same with what other attention layers add: `dist_bias` float32 [nq, dist_len], a learned bias by distance in
+// the exp2 domain (the table times log2 e), row min(i - j, dist_len - 1) of a head added to the scaled score of
+// query i and key j; `head_gate` float32, one value per (token, head) at [token * gate_stride + gate_off + head],
+// whose sigmoid multiplies the head's output; `out_scale`; the output row as a column range of a wider buffer.
+extern "C" int llm_paged_attention_prefill_ex(
+    const void* q, void* out, const void* cache, const int32_t* tiles, int n_tiles, const int32_t* entry_slot,
+    const int32_t* entry_q_start, const int32_t* entry_q_len, const int32_t* entry_kv_len,
+    const int32_t* block_table, int table_stride, int nq, int nkv, int d, int page_size, int window, float scale,
+    int num_pages, int32_t* status, const float* dist_bias, int dist_len, const float* head_gate, long long gate_stride,
+    int gate_off, float out_scale, long long out_stride, int out_off, uintptr_t stream) {
     if (n_tiles <= 0) return LLM_OK;
     if (nq <= 0 || nkv <= 0 || nq % nkv != 0 || page_size <= 0 || !llm_paged_prefill_supported(d)) return LLM_REFUSED_SIZE;
-    if (!aligned16(q) || !aligned16(out) || !aligned16(cache)) return LLM_REFUSED_ALIGN;
+    if (dist_bias && dist_len <= 0) return LLM_REFUSED_SIZE;
+    if (!aligned16(q) || !aligned16(out) || !aligned16(cache) || out_stride % 2 || out_off % 2) return LLM_REFUSED_ALIGN;
     const size_t smem = static_cast<size_t>(AP_BM + 4 * AP_BN) * d * sizeof(bf16);
     cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
     dim3 grid(nq, n_tiles);
@@ -290,7 +325,8 @@ extern "C" int llm_paged_attention_prefill(
         launch_pdl(kern, dim3(grid), dim3(AP_THREADS), smem, s, static_cast<const bf16*>(q), static_cast<bf16*>(out),              \
                                             static_cast<const bf16*>(cache), tiles, entry_slot, entry_q_start, \
                                             entry_q_len, entry_kv_len, block_table, table_stride, nq, nkv,     \
-                                            page_size, window, scale_log2e, num_pages, status);                \
+                                            page_size, window, scale_log2e, num_pages, status, dist_bias,      \
+                                            dist_len, head_gate, gate_stride, gate_off, out_scale, out_stride, out_off); \
     }
     if (d == 64) LAUNCH(64) else LAUNCH(128)
 #undef LAUNCH

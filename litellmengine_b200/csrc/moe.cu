@@ -113,49 +113,72 @@ extern "C" int llm_moe_route(const void* x, int x_dtype, const float* wr, float*
     return launch_status();
 }
 
-template <typename TO>
+__device__ __forceinline__ void moe_store4(float* p, const float (&v)[4]) { *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]); }
+__device__ __forceinline__ void moe_store4(bf16* p, const float (&v)[4]) {
+    uint2 raw;
+    __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&raw);
+    h[0] = __floats2bfloat162_rn(v[0], v[1]);
+    h[1] = __floats2bfloat162_rn(v[2], v[3]);
+    *reinterpret_cast<uint2*>(p) = raw;
+}
+
+// One block row per (token, expert): the token's weight for the expert is read once; a thread makes VEC
+// neighbouring features (VEC = 4: sixteen-byte loads of the gate and up values, which are only touched
+// for experts that were chosen; the others' columns are zeroed).
+template <typename TO, int VEC>
 __global__ void moe_act_kernel(const float* __restrict__ gu, int parts, long long part_stride,
                                const float* __restrict__ dense, TO* __restrict__ act, int E, int ff, float limit,
-                               float alpha, long long total) {
+                               float alpha) {
     pdl_begin();
-    const long long idx = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
-    if (idx >= total) return;
-    const long long row = idx / (static_cast<long long>(E) * ff);
-    const int rest = static_cast<int>(idx - row * E * ff);
-    const int e = rest / ff, f = rest - e * ff;
-    const float w = dense[row * E + e];
-    float out = 0.0f;
+    const long long pair = blockIdx.x;                  // token * E + expert
+    const int f = (blockIdx.y * blockDim.x + threadIdx.x) * VEC;
+    if (f >= ff) return;
+    const float w = dense[pair];
+    float out[4] = {0.0f, 0.0f, 0.0f, 0.0f};
     if (w != 0.0f) {
-        const float* p = gu + (row * E + e) * 2 * ff;
-        float g = 0.0f, u = 0.0f;
+        const float* p = gu + pair * 2 * ff;
+        float g[4] = {0.0f, 0.0f, 0.0f, 0.0f}, u[4] = {0.0f, 0.0f, 0.0f, 0.0f};
         for (int k = 0; k < parts; ++k) {                   // the product may come as its k-splits
-            g += p[k * part_stride + f];
-            u += p[k * part_stride + ff + f];
+            if (VEC == 4) {
+                const float4 a = *reinterpret_cast<const float4*>(p + k * part_stride + f);
+                const float4 b = *reinterpret_cast<const float4*>(p + k * part_stride + ff + f);
+                g[0] += a.x; g[1] += a.y; g[2] += a.z; g[3] += a.w;
+                u[0] += b.x; u[1] += b.y; u[2] += b.z; u[3] += b.w;
+            } else {
+                g[0] += p[k * part_stride + f];
+                u[0] += p[k * part_stride + ff + f];
+            }
         }
-        g = fminf(g, limit);
-        u = fminf(fmaxf(u, -limit), limit);
-        out = w * (g / (1.0f + expf(-alpha * g))) * (u + 1.0f);
+#pragma unroll
+        for (int c = 0; c < VEC; ++c) {
+            const float gc = fminf(g[c], limit), uc = fminf(fmaxf(u[c], -limit), limit);
+            out[c] = w * (gc / (1.0f + expf(-alpha * gc))) * (uc + 1.0f);
+        }
     }
-    act[idx] = from_f32<TO>(out);
+    TO* o = act + pair * ff + f;
+    if (VEC == 4) moe_store4(o, out);
+    else o[0] = from_f32<TO>(out[0]);
 }
 
 extern "C" int llm_moe_act(const float* gu, int parts, long long part_stride, const float* dense, void* act,
                            int act_dtype, int num_tokens, int E, int ff, float limit, float alpha, uintptr_t stream) {
     if (num_tokens <= 0) return LLM_OK;
     if (E <= 0 || ff <= 0 || !(limit > 0.0f)) return LLM_REFUSED_SIZE;
-    const long long total = static_cast<long long>(num_tokens) * E * ff;
-    const long long blocks = (total + 255) / 256;
-    if (blocks > 0x7fffffffLL) return LLM_REFUSED_SIZE;
+    const long long pairs = static_cast<long long>(num_tokens) * E;
+    if (pairs > 0x7fffffffLL) return LLM_REFUSED_SIZE;
     if (parts < 1) parts = 1;
+    const bool vec = ff % 4 == 0 && aligned16(gu) && aligned16(act) && part_stride % 4 == 0;
+    const int per_block = 128 * (vec ? 4 : 1);
+    const dim3 grid(static_cast<unsigned>(pairs), (ff + per_block - 1) / per_block);
+    if (grid.y > 65535) return LLM_REFUSED_SIZE;
     cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
-    if (act_dtype == LLM_DT_F32)
-        launch_pdl((moe_act_kernel<float>), dim3(static_cast<unsigned>(blocks)), dim3(256), 0, s, gu, parts, part_stride,
-                   dense, static_cast<float*>(act), E, ff, limit, alpha, total);
-    else if (act_dtype == LLM_DT_BF16)
-        launch_pdl((moe_act_kernel<bf16>), dim3(static_cast<unsigned>(blocks)), dim3(256), 0, s, gu, parts, part_stride,
-                   dense, static_cast<bf16*>(act), E, ff, limit, alpha, total);
-    else
-        return LLM_REFUSED_DTYPE;
+#define LAUNCH(TO, V)                                                                                          \
+    launch_pdl((moe_act_kernel<TO, V>), grid, dim3(128), 0, s, gu, parts, part_stride, dense, static_cast<TO*>(act), E, ff, \
+               limit, alpha)
+    if (act_dtype == LLM_DT_F32) { if (vec) LAUNCH(float, 4); else LAUNCH(float, 1); }
+    else if (act_dtype == LLM_DT_BF16) { if (vec) LAUNCH(bf16, 4); else LAUNCH(bf16, 1); }
+    else return LLM_REFUSED_DTYPE;
+#undef LAUNCH
     return launch_status();
 }
 
@@ -168,22 +191,69 @@ extern "C" int llm_moe_act(const float* gu, int parts, long long part_stride, co
 //   moe_down_sparse_kernel      out[token, n] = sum over the token's choices of W_down[e][n, :] . act[pair, :]
 // Weights: `w_gate_up` [E * 2 * ff, W] (per expert ff gate rows, then ff up rows) and `w_down` [W, E * ff].
 #define MOE_SPARSE_WARPS 8
-#define MOE_SPARSE_FEATURES 32
+#define MOE_SPARSE_FEATURES 8
+
+// Two rows against one vector, their loads in flight together.
+template <typename TW>
+__device__ __forceinline__ void moe_dot2(const TW* __restrict__ w0, const TW* __restrict__ w1, const float* __restrict__ xs,
+                                         int n, int lane, bool vec, float& r0, float& r1) {
+    float a0 = 0.0f, a1 = 0.0f;
+    if (vec) {
+        for (int i = lane * 8; i < n; i += 512) {
+            float p[8], q[8], p2[8], q2[8];
+            const bool more = i + 256 < n;
+            load8(w0 + i, p);
+            load8(w1 + i, q);
+            if (more) {
+                load8(w0 + i + 256, p2);
+                load8(w1 + i + 256, q2);
+            }
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                a0 += p[u] * xs[i + u];
+                a1 += q[u] * xs[i + u];
+            }
+            if (more) {
+#pragma unroll
+                for (int u = 0; u < 8; ++u) {
+                    a0 += p2[u] * xs[i + 256 + u];
+                    a1 += q2[u] * xs[i + 256 + u];
+                }
+            }
+        }
+    } else {
+        for (int i = lane; i < n; i += 32) {
+            a0 += to_f32(w0[i]) * xs[i];
+            a1 += to_f32(w1[i]) * xs[i];
+        }
+    }
+    r0 = warp_sum(a0);
+    r1 = warp_sum(a1);
+}
 
 template <typename TW>
 __device__ __forceinline__ float moe_dot(const TW* __restrict__ w, const float* __restrict__ xs, int n, int lane, bool vec) {
-    float acc = 0.0f;
+    float acc = 0.0f, acc2 = 0.0f;
     if (vec) {
-        for (int i = lane * 8; i < n; i += 256) {
-            float a[8];
-            load8(w + i, a);
+        for (int i = lane * 8; i < n; i += 1024) {           // up to four sixteen-byte loads in flight a lane
+            float p[4][8];
 #pragma unroll
-            for (int u = 0; u < 8; ++u) acc += a[u] * xs[i + u];
+            for (int j = 0; j < 4; ++j)
+                if (i + 256 * j < n) load8(w + i + 256 * j, p[j]);
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+                if (i + 256 * j < n) {
+#pragma unroll
+                    for (int u = 0; u < 8; u += 2) {
+                        acc += p[j][u] * xs[i + 256 * j + u];
+                        acc2 += p[j][u + 1] * xs[i + 256 * j + u + 1];
+                    }
+                }
         }
     } else {
         for (int i = lane; i < n; i += 32) acc += to_f32(w[i]) * xs[i];
     }
-    return warp_sum(acc);
+    return warp_sum(acc + acc2);
 }
 
 template <typename TX, typename TW, typename TO>
@@ -203,8 +273,8 @@ __global__ void moe_gate_up_sparse_kernel(const TX* __restrict__ x, const TW* __
         float out = 0.0f;
         if (e >= 0) {
             const TW* gr = wgu + (static_cast<size_t>(e) * 2 * ff + f) * W;
-            float g = moe_dot(gr, xs, W, lane, vec);
-            float u = moe_dot(gr + static_cast<size_t>(ff) * W, xs, W, lane, vec);
+            float g, u;
+            moe_dot2(gr, gr + static_cast<size_t>(ff) * W, xs, W, lane, vec, g, u);
             g = fminf(g, limit);
             u = fminf(fmaxf(u, -limit), limit);
             out = wt * (g / (1.0f + expf(-alpha * g))) * (u + 1.0f);

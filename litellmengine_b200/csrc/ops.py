@@ -491,13 +491,15 @@ def paged_attention_generic_kv(q: torch.Tensor, keys: torch.Tensor, values: torc
                                page_size: int, window: Optional[int], scale: float, status: torch.Tensor,
                                out: torch.Tensor, out_off: int = 0, gate: Optional[torch.Tensor] = None,
                                gate_off: int = 0, out_scale: float = 1.0, dist_bias: Optional[torch.Tensor] = None,
-                               gate_per_head: bool = False) -> torch.Tensor:
+                               gate_per_head: bool = False, rows: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Causal attention of every token in q [T, nq*dk] over its request's pages of `keys` [pages, nkv, page,
     dk] and `values` [pages, nkv, page, dv] (views with any page stride), written into columns out_off ..
     out_off + nq*dv of `out`, times sigmoid(gate[:, gate_off + ...]) (float32, optional; one value per output
     channel, or per head with `gate_per_head`) and `out_scale`.  `dist_bias` (float32 [len, nq]): row min(i - j,
-    len - 1) is added to the scaled scores of query i and key j."""
-    _dev(q, positions, token_entry, entry_slot, block_table, status, dist_bias)
+    len - 1) is added to the scaled scores of query i and key j.  `rows` (int32): only these tokens are worked on
+    (-1 entries are padding)."""
+    _dev(q, positions, token_entry, entry_slot, block_table, status, dist_bias, rows)
+    _i32(rows, "rows")
     if dist_bias is not None and (dist_bias.dtype != torch.float32 or dist_bias.dim() != 2 or dist_bias.shape[1] != nq):
         raise KernelError("dist_bias must be float32 [distances, heads]")
     T = q.shape[0]
@@ -512,13 +514,14 @@ def paged_attention_generic_kv(q: torch.Tensor, keys: torch.Tensor, values: torc
     f = _fn("attention_generic", "llm_paged_attention_generic_kv",
             [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_longlong, c_longlong, c_void_p, c_void_p, c_void_p,
              c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_longlong,
-             c_int, c_float, c_longlong, c_int, c_void_p, c_void_p, c_int, c_int, c_void_p])
+             c_int, c_float, c_longlong, c_int, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p])
     _check(f(_ptr(q), _ptr(out), _dt(q), _ptr(keys), _ptr(values), _dt(keys), keys.stride(0), values.stride(0),
-             _ptr(positions), _ptr(token_entry), _ptr(entry_slot), _ptr(block_table), block_table.shape[1], T, nq, nkv,
+             _ptr(positions), _ptr(token_entry), _ptr(entry_slot), _ptr(block_table), block_table.shape[1],
+             rows.numel() if rows is not None else T, nq, nkv,
              dk, dv, page_size, int(window) if window else 0, float(scale), keys.shape[0], _ptr(gate),
              gate.stride(0) if gate is not None else 0, gate_off, float(out_scale), out.stride(0), out_off,
              _ptr(status), _ptr(dist_bias), dist_bias.shape[0] if dist_bias is not None else 0,
-             1 if gate_per_head else 0, _stream()), "paged_attention_generic_kv")
+             1 if gate_per_head else 0, _ptr(rows), _stream()), "paged_attention_generic_kv")
     return out
 
 
@@ -898,6 +901,45 @@ def paged_attention_prefill(q: torch.Tensor, out: torch.Tensor, cache: torch.Ten
              _ptr(entry_q_len), _ptr(entry_kv_len), _ptr(block_table), block_table.shape[1], nq, nkv, d,
              page_size, int(window) if window else 0, float(scale), cache.shape[0], _ptr(status), _stream()),
            "paged_attention_prefill")
+    return out
+
+
+def prefill_attention_supported(d: int) -> bool:
+    """Whether the tensor-core kernel for prompt portions (`paged_attention_prefill*`) takes this head size."""
+    if d % 64 != 0:
+        return False
+    return bool(_fn("attention_prefill", "llm_paged_prefill_supported", [c_int])(d))
+
+
+def paged_attention_prefill_biased(q: torch.Tensor, out: torch.Tensor, out_off: int, cache: torch.Tensor, tiles: torch.Tensor,
+                                   n_tiles: int, entry_slot, entry_q_start, entry_q_len, entry_kv_len,
+                                   block_table: torch.Tensor, nq: int, nkv: int, d: int, page_size: int,
+                                   window: Optional[int], scale: float, status: torch.Tensor,
+                                   dist_bias_t: Optional[torch.Tensor] = None, head_gate: Optional[torch.Tensor] = None,
+                                   gate_off: int = 0, out_scale: float = 1.0) -> torch.Tensor:
+    """`paged_attention_prefill` with what other attention layers add: `dist_bias_t` float32 [nq, distances], a bias by
+    distance TIMES log2(e) (row min(i - j, distances - 1) of the head joins the scaled score); `head_gate` float32
+    [T, ...] with one value per (token, head) from column gate_off, whose sigmoid multiplies the head's output;
+    `out_scale`; the result goes to columns out_off .. out_off + nq*d of `out` (bfloat16, any row stride)."""
+    _dev(q, cache, tiles, entry_slot, entry_q_start, entry_q_len, entry_kv_len, block_table, status, dist_bias_t)
+    if q.dtype != torch.bfloat16 or cache.dtype != torch.bfloat16 or out.dtype != torch.bfloat16 or out.stride(1) != 1:
+        raise KernelError("the prefill attention kernel is bfloat16 only")
+    if q.shape[1] != nq * d or tuple(cache.shape[1:]) != (2, nkv, page_size, d):
+        raise KernelError("q must be [T, heads*head_dim] and cache [pages, 2, kv_heads, page_size, head_dim]")
+    if dist_bias_t is not None and (dist_bias_t.dtype != torch.float32 or dist_bias_t.dim() != 2 or dist_bias_t.shape[0] != nq):
+        raise KernelError("dist_bias_t must be float32 [heads, distances]")
+    if head_gate is not None and (head_gate.dtype != torch.float32 or head_gate.stride(1) != 1):
+        raise KernelError("head_gate must be float32 with unit stride along rows")
+    f = _fn("attention_prefill", "llm_paged_attention_prefill_ex",
+            [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+             c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_void_p, c_int, c_void_p, c_longlong, c_int,
+             c_float, c_longlong, c_int, c_void_p])
+    _check(f(_ptr(q), _ptr(out), _ptr(cache), _ptr(tiles), n_tiles, _ptr(entry_slot), _ptr(entry_q_start),
+             _ptr(entry_q_len), _ptr(entry_kv_len), _ptr(block_table), block_table.shape[1], nq, nkv, d,
+             page_size, int(window) if window else 0, float(scale), cache.shape[0], _ptr(status), _ptr(dist_bias_t),
+             dist_bias_t.shape[1] if dist_bias_t is not None else 0, _ptr(head_gate),
+             head_gate.stride(0) if head_gate is not None else 0, gate_off, float(out_scale), out.stride(0), out_off,
+             _stream()), "paged_attention_prefill_biased")
     return out
 
 

@@ -276,6 +276,12 @@ class GatedAttentionMixer(BranchMixer):
         self._tuned = (compute_dtype == torch.bfloat16 and self.dv == self.d and self.device.type == "cuda"
                        and spec.distance_bias is None and not self.gate_per_head
                        and ops.fast_attention_supported(self.d, self.nq // self.nkv))
+        # with a bias by distance or a gate per head: prompt portions still take a tensor-core kernel (the
+        # mma.sync one, which adds the bias to its scores and gates as it stores), single tokens the general one
+        self._tuned_prompt = (not self._tuned and compute_dtype == torch.bfloat16 and self.dv == self.d
+                              and self.device.type == "cuda" and (self.gate_per_head or not spec.output_gate)
+                              and ops.prefill_attention_supported(self.d))
+        self.dist_table_t = None
 
     def parameters(self) -> Dict[str, ParamSpec]:
         n, s = self.names, self.spec
@@ -315,6 +321,8 @@ class GatedAttentionMixer(BranchMixer):
                 count = min(count, s.window)
             index = torch.tensor([distance_bucket(d, rows, far) for d in range(count)], dtype=torch.long, device=rel.device)
             self.dist_table = rel[index].contiguous()
+            # for the tensor-core kernel: a row per head, in the exp2 domain
+            self.dist_table_t = (self.dist_table.t() * math.log2(math.e)).contiguous()
         ops.prepare_streaming(self.w_in)
         ops.prepare_streaming(self.w_o)
 
@@ -322,7 +330,7 @@ class GatedAttentionMixer(BranchMixer):
         return PagedNeed(self.nkv, self.d, self.spec.window, None if self.dv == self.d else self.dv)
 
     def step_prelude(self):
-        return AttentionWork() if self._tuned else None
+        return AttentionWork() if self._tuned or self._tuned_prompt else None
 
     @property
     def graph_variant_group(self):
@@ -346,11 +354,26 @@ class GatedAttentionMixer(BranchMixer):
             a = attention_over_pages(q, ctx, self.nq, self.nkv, self.d, s.window, self.scale)
             ops.gate_mul(a, proj, col0 + self.g_off, out, out_col0, s.output_gate, out_scale)
             return
+        work = b.preludes.get(AttentionWork.name) if self._tuned_prompt and ctx.cache is not None else None
+        padded = getattr(b, "any_division", False)
+        if work is not None and (padded or work.num_prefill_tiles):
+            # prompt portions on the tensor cores, the step's single tokens (if any) in the general kernel
+            n_tiles = work.padded_tiles.shape[0] if padded else work.num_prefill_tiles
+            ops.paged_attention_prefill_biased(
+                q, out, out_col0, ctx.cache, work.padded_tiles if padded else work.prefill_tiles, n_tiles, b.entry_slot,
+                b.entry_q_start, b.entry_q_len, b.entry_kv_len, ctx.block_table, self.nq, self.nkv, self.d, ctx.page_size,
+                s.window, self.scale, ctx.status, dist_bias_t=self.dist_table_t, head_gate=proj if s.output_gate else None,
+                gate_off=col0 + self.g_off, out_scale=out_scale)
+            rows = work.padded_rows if padded else (work.decode_rows if work.num_decode else None)
+            if rows is None:
+                return
+        else:
+            rows = None
         ops.paged_attention_generic_kv(
             q, ctx.cache_keys, ctx.cache_values, b.positions, b.token_entry, b.entry_slot, ctx.block_table, self.nq,
             self.nkv, self.d, self.dv, ctx.page_size, s.window, self.scale, ctx.status, out, out_col0,
             gate=proj if s.output_gate else None, gate_off=col0 + self.g_off, out_scale=out_scale,
-            dist_bias=self.dist_table, gate_per_head=self.gate_per_head)
+            dist_bias=self.dist_table, gate_per_head=self.gate_per_head, rows=rows)
 
 
 def distance_bucket(n: int, rows: int, far: float) -> int:

@@ -520,3 +520,47 @@ def test_expert_activation_and_routed_sum():
     for rows in (50, 3, 2):      # a prompt portion, decode steps (the last one reads only the chosen experts)
         got = _ops().as_tensor(part.forward(x[:rows].float().to(DEV).contiguous()))
         assert (got.double().cpu() - ref[:rows]).abs().max() < 2e-5
+
+
+@pytest.mark.parametrize("d,window", [(64, None), (64, 70), (128, 33), (128, 200)])
+def test_tensor_core_prompt_attention_with_distance_bias_and_head_gate(d, window):
+    """The kernel that prompt portions of a bfloat16 run take (head sizes 64 and 128): a portion that starts in the
+    middle of a page with keys before it, a table that matters, a key that would win placed just inside and just
+    outside the window, a gate per head, the output as columns of a wider buffer; the step's single token goes
+    through the general kernel by a row list."""
+    ops = _ops()
+    from litellmengine_b200.parts.attention import distance_bucket
+    N, past, page, H, G, rows_, far, scale = 300, 37, 16, 4, 2, 12, 90.0, 0.2
+    T = N - past
+    g = torch.Generator().manual_seed(d + (window or 0))
+    q, k, v = (torch.randn(N, n, d, generator=g, dtype=F64) for n in (H, G, G))
+    rel = torch.randn(rows_, H, generator=g, dtype=F64) * 2
+    gate = torch.randn(N, H, generator=g, dtype=F64)
+    if window is not None:
+        for i, off in ((299, window - 1), (298, window), (200, window - 1), (150, window)):
+            k[i - off] = q[i, :G] * (2.0 if d == 64 else 1.4)
+    q, k, v = (t.to(torch.bfloat16).double() for t in (q, k, v))
+    ref = pg.attention_core(q[past:], k, v, rel, scale, far, window, first_position=past) * torch.sigmoid(gate[past:])[:, :, None]
+    count = int(math.ceil(far)) + 1 if window is None else min(int(math.ceil(far)) + 1, window)
+    table = rel[[distance_bucket(n, rows_, far) for n in range(count)]].float().to(DEV).contiguous()
+    table_t = (table.t() * math.log2(math.e)).contiguous()
+    keys, values, block_table, order = _paged(N, page, G, d, d, torch.bfloat16, 2)
+    cache = torch.zeros(keys.shape[0], 2, G, page, d, dtype=torch.bfloat16, device=DEV)
+    _fill(cache[:, 0], cache[:, 1], order, page, k, v)
+    qd = q[past:].reshape(T, -1).to(torch.bfloat16).to(DEV)
+    out = torch.zeros(T, H * d + 16, dtype=torch.bfloat16, device=DEV)
+    gate_buf = torch.zeros(T, 5 + H, dtype=torch.float32, device=DEV)
+    gate_buf[:, 5:] = gate[past:].float().to(DEV)
+    status = torch.zeros(2, dtype=torch.int32, device=DEV)
+    # the portion is entry 0 (its last row left to the general kernel as if it were another entry's single token)
+    tiles = _i32([(0, r0) for r0 in range(0, T - 1, ops.PREFILL_TILE_ROWS)])
+    ops.paged_attention_prefill_biased(qd, out, 16, cache, tiles, tiles.shape[0], _i32([1]), _i32([0]), _i32([T - 1]), _i32([N - 1]),
+                                       block_table, H, G, d, page, window, scale, status, dist_bias_t=table_t, head_gate=gate_buf,
+                                       gate_off=5, out_scale=1.0)
+    ops.paged_attention_generic_kv(qd, cache[:, 0], cache[:, 1], _i32(list(range(past, N))), _i32([0] * T), _i32([1]), block_table,
+                                   H, G, d, d, page, window, scale, status, out, 16, gate=gate_buf, gate_off=5, dist_bias=table,
+                                   gate_per_head=True, rows=_i32([T - 1, -1]))
+    assert status.tolist() == [0, 0]
+    got = out[:, 16:].double().cpu().view(T, H, d)
+    assert (got - ref).abs().max() < 0.06
+    assert float(out[:, :16].abs().max()) == 0.0
