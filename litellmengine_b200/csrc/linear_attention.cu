@@ -385,7 +385,10 @@ __global__ void __launch_bounds__(MAX_THREADS) gla_scan_kernel(
 // per thread, at most 65,536).  States too large for that (128 x 256 a head and more) take R = 64 compiled
 // for 512 or 1,024 threads: the compiler then keeps part of the state in local memory, which is slow and
 // correct.
-static int gla_rows_per_thread(int D, int V, int* dg_out, int* max_threads) {
+// `wide32`: a block of up to 544 threads at 32 rows a thread is allowed (17 warps: a state of 128 x 128 with one
+// more column, the normaliser of a matrix memory, is 4 row groups x 129 columns = 516 threads; at 64 rows a
+// thread it would run half as fast).
+static int gla_rows_per_thread(int D, int V, int* dg_out, int* max_threads, bool wide32 = false) {
     const int cands[4] = {8, 16, 32, 64};
     const int limits[2][4] = {{512, 512, 512, 384}, {1024, 1024, 512, 384}};
     const int compiled_for[4] = {1024, 1024, 512, 384};
@@ -409,6 +412,11 @@ static int gla_rows_per_thread(int D, int V, int* dg_out, int* max_threads) {
                 *dg_out = dg;
                 *max_threads = compiled_for[c];
                 return cands[c];
+            }
+            if (wide32 && cands[c] == 32 && static_cast<long long>(V) * dg <= 544) {
+                *dg_out = dg;
+                *max_threads = 544;
+                return 32;
             }
         }
     const int dg = (D + 63) / 64;
@@ -448,7 +456,7 @@ extern "C" int llm_recur_scan(
     const int VC = V + (nfloor ? 1 : 0);
     if (state_head_stride < static_cast<long long>(D) * VC) return LLM_REFUSED_SIZE;
     int DG = 0, MT = 0;
-    const int R = gla_rows_per_thread(D, VC, &DG, &MT);
+    const int R = gla_rows_per_thread(D, VC, &DG, &MT, decay_kind == 1);
     if (R == 0) return LLM_REFUSED_SIZE;
     const size_t per_buf = decay_kind ? (2 * static_cast<size_t>(D) + V + 2) : (3 * static_cast<size_t>(D) + V);
     const size_t smem = static_cast<size_t>(GLA_TB) * (2 * per_buf + static_cast<size_t>(DG) * VC) * sizeof(float);
@@ -482,9 +490,12 @@ extern "C" int llm_recur_scan(
             else LAUNCH(64, 1024, TO, SC);                                                                        \
             break;                                                                                                \
     }
-    if (out_dtype == LLM_DT_F32) { if (decay_kind) { BY_R(float, true) } else { BY_R(float, false) } }
-    else if (out_dtype == LLM_DT_BF16) { if (decay_kind) { BY_R(bf16, true) } else { BY_R(bf16, false) } }
-    else return LLM_REFUSED_DTYPE;
+    if (out_dtype != LLM_DT_F32 && out_dtype != LLM_DT_BF16) return LLM_REFUSED_DTYPE;
+    if (R == 32 && MT == 544) {
+        if (out_dtype == LLM_DT_F32) LAUNCH(32, 544, float, true);
+        else LAUNCH(32, 544, bf16, true);
+    } else if (out_dtype == LLM_DT_F32) { if (decay_kind) { BY_R(float, true) } else { BY_R(float, false) } }
+    else { if (decay_kind) { BY_R(bf16, true) } else { BY_R(bf16, false) } }
 #undef BY_R
 #undef LAUNCH
     return launch_status();

@@ -333,3 +333,163 @@ extern "C" int llm_moe_sparse(const void* x, int x_dtype, const void* wgu, const
     }
     return launch_status();
 }
+
+// ---- prompt portions: tokens sorted by expert around the library's grouped matrix product -------------------
+// moe_sort_kernel      (one block) counts the (token, choice) pairs of each expert, lays the experts' rows one
+//                      after another and gives every pair its row: offs[e] = end of expert e's rows, pos[pair] =
+//                      the pair's row, row_pair[row] = the pair (token = pair / top).  Which of an expert's
+//                      rows a pair gets is not fixed; no result depends on it (a row's products are its own).
+// moe_gather_kernel    xs[row] = x[token of the row]
+// moe_act_pairs_kernel act[row, f] = w * g * sigmoid(alpha g) * (u + 1) from the grouped product's [rows, 2 ff]
+// moe_combine_kernel   out[token] = sum over its choices of y[pos[pair]], in 32-bit, in the order of the choices
+__global__ void moe_sort_kernel(const int32_t* __restrict__ ids, int pairs, int E, int32_t* __restrict__ offs,
+                                int32_t* __restrict__ pos, int32_t* __restrict__ row_pair) {
+    pdl_begin();
+    extern __shared__ int sort_smem[];
+    int* hist = sort_smem;            // [E]
+    int* base = hist + E;             // [E]
+    for (int e = threadIdx.x; e < E; e += blockDim.x) hist[e] = 0;
+    __syncthreads();
+    for (int p = threadIdx.x; p < pairs; p += blockDim.x) {
+        const int e = ids[p];
+        if (e >= 0 && e < E) atomicAdd(&hist[e], 1);
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int run = 0;
+        for (int e = 0; e < E; ++e) {
+            base[e] = run;
+            run += hist[e];
+            offs[e] = run;
+            hist[e] = 0;              // becomes the cursor
+        }
+    }
+    __syncthreads();
+    for (int p = threadIdx.x; p < pairs; p += blockDim.x) {
+        const int e = ids[p];
+        if (e >= 0 && e < E) {
+            const int r = base[e] + atomicAdd(&hist[e], 1);
+            pos[p] = r;
+            row_pair[r] = p;
+        } else {
+            pos[p] = -1;
+        }
+    }
+}
+
+template <typename T>
+__global__ void moe_gather_kernel(const T* __restrict__ x, const int32_t* __restrict__ row_pair, T* __restrict__ xs,
+                                  int W, int top, int vec) {
+    pdl_begin();
+    const long long r = blockIdx.x;
+    const T* src = x + static_cast<size_t>(row_pair[r] / top) * W;
+    T* dst = xs + r * W;
+    if (vec) {
+        constexpr int PER = 16 / sizeof(T);
+        for (int i = threadIdx.x * PER; i < W; i += blockDim.x * PER)
+            *reinterpret_cast<uint4*>(dst + i) = *reinterpret_cast<const uint4*>(src + i);
+    } else {
+        for (int i = threadIdx.x; i < W; i += blockDim.x) dst[i] = src[i];
+    }
+}
+
+template <typename T>
+__global__ void moe_act_pairs_kernel(const T* __restrict__ gu, const int32_t* __restrict__ row_pair,
+                                     const float* __restrict__ weights, T* __restrict__ act, int ff, float limit,
+                                     float alpha, int vec) {
+    pdl_begin();
+    const long long r = blockIdx.x;
+    const float w = weights[row_pair[r]];
+    const T* g = gu + r * 2 * ff;
+    T* o = act + r * ff;
+    if (vec) {
+        for (int f = (blockIdx.y * blockDim.x + threadIdx.x) * 8; f < ff; f += gridDim.y * blockDim.x * 8) {
+            float a[8], b[8];
+            load8(g + f, a);
+            load8(g + ff + f, b);
+#pragma unroll
+            for (int c = 0; c < 8; ++c) {
+                const float gc = fminf(a[c], limit), uc = fminf(fmaxf(b[c], -limit), limit);
+                a[c] = w * (gc / (1.0f + expf(-alpha * gc))) * (uc + 1.0f);
+            }
+            store8(o + f, a);
+        }
+    } else {
+        for (int f = blockIdx.y * blockDim.x + threadIdx.x; f < ff; f += gridDim.y * blockDim.x) {
+            const float gc = fminf(to_f32(g[f]), limit), uc = fminf(fmaxf(to_f32(g[ff + f]), -limit), limit);
+            o[f] = from_f32<T>(w * (gc / (1.0f + expf(-alpha * gc))) * (uc + 1.0f));
+        }
+    }
+}
+
+template <typename T>
+__global__ void moe_combine_kernel(const T* __restrict__ y, const int32_t* __restrict__ pos, float* __restrict__ out,
+                                   int W, int top, int vec) {
+    pdl_begin();
+    const long long t = blockIdx.x;
+    if (vec) {
+        for (int i = (blockIdx.y * blockDim.x + threadIdx.x) * 8; i < W; i += gridDim.y * blockDim.x * 8) {
+            float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+            for (int k = 0; k < top; ++k) {
+                const int r = pos[t * top + k];
+                if (r < 0) continue;
+                float a[8];
+                load8(y + static_cast<size_t>(r) * W + i, a);
+#pragma unroll
+                for (int c = 0; c < 8; ++c) acc[c] += a[c];
+            }
+            store8(out + t * W + i, acc);
+        }
+    } else {
+        for (int i = blockIdx.y * blockDim.x + threadIdx.x; i < W; i += gridDim.y * blockDim.x) {
+            float acc = 0.0f;
+            for (int k = 0; k < top; ++k) {
+                const int r = pos[t * top + k];
+                if (r >= 0) acc += to_f32(y[static_cast<size_t>(r) * W + i]);
+            }
+            out[t * W + i] = acc;
+        }
+    }
+}
+
+extern "C" int llm_moe_sort(const int32_t* ids, int pairs, int E, int32_t* offs, int32_t* pos, int32_t* row_pair,
+                            uintptr_t stream) {
+    if (pairs <= 0) return LLM_OK;
+    if (E <= 0 || E > 4096) return LLM_REFUSED_SIZE;
+    launch_pdl(moe_sort_kernel, dim3(1), dim3(1024), 2 * E * sizeof(int), reinterpret_cast<cudaStream_t>(stream), ids, pairs,
+               E, offs, pos, row_pair);
+    return launch_status();
+}
+
+// which = 0: gather (a = x [T, W], out = xs [pairs, W]); 1: activation (a = gu [pairs, 2 n], out = act [pairs, n]);
+// 2: combine (a = y [pairs, n], out = float32 [T, n], index = pos).  n is the row width of `out`.
+extern "C" int llm_moe_rows(int which, const void* a, int dtype, const int32_t* index, const float* weights, void* out,
+                            int rows, int n, int top, float limit, float alpha, uintptr_t stream) {
+    if (rows <= 0) return LLM_OK;
+    if (n <= 0 || top <= 0 || which < 0 || which > 2) return LLM_REFUSED_SIZE;
+    const int esz = dtype == LLM_DT_F32 ? 4 : 2;
+    const int vec = (n % 8 == 0) && aligned16(a) && aligned16(out) && (static_cast<long long>(n) * esz) % 16 == 0;
+    cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+    const int gy = which == 0 ? 1 : (n + 128 * 8 - 1) / (128 * 8);
+    const dim3 grid(rows, gy), block(128);
+    if (which == 0) {
+        if (dtype == LLM_DT_F32) launch_pdl((moe_gather_kernel<float>), grid, block, 0, s, static_cast<const float*>(a), index,
+                                            static_cast<float*>(out), n, top, vec);
+        else if (dtype == LLM_DT_BF16) launch_pdl((moe_gather_kernel<bf16>), grid, block, 0, s, static_cast<const bf16*>(a), index,
+                                                  static_cast<bf16*>(out), n, top, vec);
+        else return LLM_REFUSED_DTYPE;
+    } else if (which == 1) {
+        if (dtype == LLM_DT_F32) launch_pdl((moe_act_pairs_kernel<float>), grid, block, 0, s, static_cast<const float*>(a), index,
+                                            weights, static_cast<float*>(out), n, limit, alpha, vec);
+        else if (dtype == LLM_DT_BF16) launch_pdl((moe_act_pairs_kernel<bf16>), grid, block, 0, s, static_cast<const bf16*>(a),
+                                                  index, weights, static_cast<bf16*>(out), n, limit, alpha, vec);
+        else return LLM_REFUSED_DTYPE;
+    } else {
+        if (dtype == LLM_DT_F32) launch_pdl((moe_combine_kernel<float>), grid, block, 0, s, static_cast<const float*>(a), index,
+                                            static_cast<float*>(out), n, top, vec);
+        else if (dtype == LLM_DT_BF16) launch_pdl((moe_combine_kernel<bf16>), grid, block, 0, s, static_cast<const bf16*>(a), index,
+                                                  static_cast<float*>(out), n, top, vec);
+        else return LLM_REFUSED_DTYPE;
+    }
+    return launch_status();
+}

@@ -827,6 +827,41 @@ def moe_sparse(x: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Tensor, i
     return out
 
 
+def grouped_product_available() -> bool:
+    """Whether the tensor library offers a grouped matrix product with row offsets on the device."""
+    return hasattr(torch, "_grouped_mm")
+
+
+def moe_sorted(x: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor,
+               E: int, ff: int, limit: float, alpha: float) -> torch.Tensor:
+    """The routed feed-forward for prompt portions: the (token, choice) pairs are sorted by expert (the engine's
+    kernels), each expert's rows go through ITS matrices in the library's grouped matrix product (bfloat16 in,
+    bfloat16 out, 32-bit accumulation; the row offsets stay on the device), the activation takes each row's
+    routing weight, and a token's rows are added in 32-bit.  Returns float32 [T, W]."""
+    _dev(x, w_gate_up, w_down, ids, weights)
+    T, W = x.shape
+    top = ids.shape[1]
+    pairs = T * top
+    dev = x.device
+    offs = torch.empty(E, dtype=torch.int32, device=dev)
+    pos = torch.empty(pairs, dtype=torch.int32, device=dev)
+    row_pair = torch.empty(pairs, dtype=torch.int32, device=dev)
+    _check(_fn("moe", "llm_moe_sort", [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p])(
+        _ptr(ids), pairs, E, _ptr(offs), _ptr(pos), _ptr(row_pair), _stream()), "moe_sort")
+    rows_fn = _fn("moe", "llm_moe_rows",
+                  [c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_float, c_void_p])
+    xs = torch.empty((pairs, W), dtype=x.dtype, device=dev)
+    _check(rows_fn(0, _ptr(x), _dt(x), _ptr(row_pair), None, _ptr(xs), pairs, W, top, 0.0, 0.0, _stream()), "moe_gather")
+    gu = torch._grouped_mm(xs, w_gate_up.view(E, 2 * ff, W).transpose(1, 2), offs=offs)
+    act = torch.empty((pairs, ff), dtype=x.dtype, device=dev)
+    _check(rows_fn(1, _ptr(gu), _dt(gu), _ptr(row_pair), _ptr(weights), _ptr(act), pairs, ff, top, float(limit), float(alpha),
+                   _stream()), "moe_act_pairs")
+    y = torch._grouped_mm(act, w_down.view(W, E, ff).permute(1, 2, 0), offs=offs)
+    out = torch.empty((T, W), dtype=torch.float32, device=dev)
+    _check(rows_fn(2, _ptr(y), _dt(y), _ptr(pos), None, _ptr(out), T, W, top, 0.0, 0.0, _stream()), "moe_combine")
+    return out
+
+
 def fast_attention_supported(d: int, group: int) -> bool:
     """Whether the tuned bfloat16 kernels (tensor-core prefill, split-key decode) take this shape."""
     if d % 64 != 0:          # they are written for head sizes 64 and 128: do not compile them just to hear "no"

@@ -61,16 +61,20 @@ class RoutedExperts:
     The result is the weighted sum of the chosen experts' outputs.
 
     The experts' [gate; up] matrices are stacked into one and their down matrices stand side by side along the
-    input axis.  Prompt portions: one product gives every expert's gate and up values, the activation kernel
-    multiplies each expert's activations by the token's weight for it (zero for experts that were not chosen) and
-    ONE down product adds the chosen experts' outputs up: tensor-core products over all experts.  Steps whose
-    (token, choice) pairs are fewer than the experts (decode steps of a model with many experts) read only the
-    chosen experts' matrices, in two kernels of their own."""
+    input axis.  Three ways to run, chosen by the step's size; all give the same sums up to rounding.
+    Prompt portions in bfloat16: the (token, choice) pairs are sorted by expert and each expert's rows go through
+    its own matrices in the library's grouped matrix product (exactly the chosen experts' flops).  Steps whose
+    pairs are fewer than the experts (decode steps of a model with many experts): two kernels that read only the
+    chosen experts' matrices.  Otherwise (decode steps that touch most experts anyway; the 32-bit mode): one
+    product gives every expert's gate and up values, the activation kernel multiplies each expert's activations
+    by the token's weight for it (zero for experts that were not chosen) and ONE down product adds the chosen
+    experts' outputs up."""
 
     graph_safe = True
     any_division_safe = True
     supports_partials = True
     ACT_ALPHA = 1.702
+    SORTED_FROM = 32           # steps of more tokens than the weight-streaming product takes sort their tokens by expert
 
     def __init__(self, spec: FeedForwardSpec, hidden_size: int, compute_dtype: torch.dtype, device):
         p = dict(spec.params)
@@ -111,6 +115,10 @@ class RoutedExperts:
                 and self.top * self.ff <= 12288):
             _, ids, weights = ops.moe_route(x, self.w_router, self.top, self.groups, self.route_scale, lists=True)
             return ops.moe_sparse(x, self.w_gate_up, self.w_down, ids, weights, self.ff, self.limit, self.ACT_ALPHA)
+        if (T > self.SORTED_FROM and x.dtype == torch.bfloat16 and self.w_gate_up.dtype == self.w_down.dtype == torch.bfloat16
+                and self.hidden % 8 == 0 and self.ff % 8 == 0 and self.E <= 4096 and ops.grouped_product_available()):
+            _, ids, weights = ops.moe_route(x, self.w_router, self.top, self.groups, self.route_scale, lists=True)
+            return ops.moe_sorted(x, self.w_gate_up, self.w_down, ids, weights, self.E, self.ff, self.limit, self.ACT_ALPHA)
         dense = ops.moe_route(x, self.w_router, self.top, self.groups, self.route_scale)
         gate_up = ops.linear(x, self.w_gate_up, out_dtype=torch.float32, partials_ok=True)
         act = ops.moe_act(gate_up, dense, self.E, self.ff, self.limit, self.ACT_ALPHA, self.dtype)

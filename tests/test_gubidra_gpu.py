@@ -443,7 +443,7 @@ def test_retention_recurrence_in_every_cutting(shape):
         assert (state.view(H, D, V) * D ** -0.5 - S).abs().max() < 3e-4 * max(1.0, float(S.abs().max())), name
 
 
-@pytest.mark.parametrize("shape", [(3, 8, 16), (2, 16, 8), (1, 64, 64), (2, 12, 20), (2, 32, 48)])
+@pytest.mark.parametrize("shape", [(3, 8, 16), (2, 16, 8), (1, 64, 64), (2, 12, 20), (2, 32, 48), (1, 128, 128)])
 def test_matrix_memory_recurrence_in_every_cutting(shape):
     """Exponential gates with a running maximum from 0: gates far out on both sides (the cap holds them), a
     normaliser below its floor at the first tokens and above it later; one pass, chunks, portions, decode."""
@@ -503,7 +503,7 @@ def test_expert_activation_and_routed_sum():
     """The whole feed-forward part against the plain code, clamps included (inputs beyond the limit on both sides)."""
     from litellmengine_b200.config.specs import FeedForwardSpec
     from litellmengine_b200.parts.feed_forward import RoutedExperts
-    W, ff, E = 32, 20, 6
+    W, ff, E = 32, 24, 6
     g = torch.Generator().manual_seed(2)
     w = {"l0.mlp.router": torch.randn(E, W, generator=g, dtype=F64) * 0.5}
     for e in range(E):
@@ -520,6 +520,20 @@ def test_expert_activation_and_routed_sum():
     for rows in (50, 3, 2):      # a prompt portion, decode steps (the last one reads only the chosen experts)
         got = _ops().as_tensor(part.forward(x[:rows].float().to(DEV).contiguous()))
         assert (got.double().cpu() - ref[:rows]).abs().max() < 2e-5
+    # bfloat16: a prompt portion sorts its tokens by expert around the grouped product; a few tokens run the other ways
+    wb = {n: t.to(torch.bfloat16).double() for n, t in w.items()}
+    xb = x.to(torch.bfloat16).double()
+    refb = pg.moe(xb, wb, "l0.mlp", mlp, act=pg.bf16_round)
+    pick, _ = pg.route(xb, wb["l0.mlp.router"], mlp["router"])
+    s_all = torch.sigmoid(xb @ wb["l0.mlp.router"].T)
+    clear = (s_all[:, :, None] - s_all[:, None, :]).abs().add(torch.eye(E) * 9).amin(dim=(1, 2)) > 2e-3
+    part16 = RoutedExperts(spec, W, torch.bfloat16, DEV)
+    part16.load({n[len("l0.mlp."):]: (t.to(torch.bfloat16) if "router" not in n else t.float()).to(DEV) for n, t in w.items()})
+    for rows in (50, 33, 3, 2):
+        got = _ops().as_tensor(part16.forward(xb[:rows].to(torch.bfloat16).to(DEV).contiguous())).double().cpu()
+        keep = clear[:rows]
+        assert keep.sum() >= rows // 2
+        assert (got - refb[:rows])[keep].abs().max() < 0.05 * float(refb.abs().max())
 
 
 @pytest.mark.parametrize("d,window", [(64, None), (64, 70), (128, 33), (128, 200)])
