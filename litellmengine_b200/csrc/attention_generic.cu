@@ -114,15 +114,27 @@ __global__ void paged_attention_generic_kernel(
 #pragma unroll
         for (int r = 0; r < AG_MAX_D / 32; ++r) acc[r] *= alpha;
         const int count = min(32, pos - base + 1);
-        for (int jj = 0; jj < count; ++jj) {
-            const float pj = __shfl_sync(0xffffffffu, p, jj);
-            const long long vo = __shfl_sync(0xffffffffu, voff, jj);
-            if (pj == 0.0f) continue;                  // also skips keys whose page was refused
-            const TC* vr = values + vo;
+        const int regs = (dv + 31) >> 5;               // value entries a lane holds
+        for (int jj = 0; jj < count; jj += 4) {       // four keys' value rows in flight: their loads do not wait for one another
+            float pj[4];
+            const TC* vr[4];
 #pragma unroll
-            for (int r = 0; r < AG_MAX_D / 32; ++r) {
+            for (int u = 0; u < 4; ++u) {
+                const float pu = __shfl_sync(0xffffffffu, p, (jj + u) & 31);
+                const long long vo = __shfl_sync(0xffffffffu, voff, (jj + u) & 31);
+                const bool use = jj + u < count && vo >= 0;     // a key whose page was refused has no row
+                pj[u] = use ? pu : 0.0f;
+                vr[u] = values + (use ? vo : 0);
+            }
+            for (int r = 0; r < regs; ++r) {
                 const int i = lane + 32 * r;
-                if (i < dv) acc[r] += pj * to_f32(vr[i]);
+                if (i < dv) {
+                    float x[4];
+#pragma unroll
+                    for (int u = 0; u < 4; ++u) x[u] = to_f32(vr[u][i]);
+#pragma unroll
+                    for (int u = 0; u < 4; ++u) acc[r] += pj[u] * x[u];
+                }
             }
         }
     }

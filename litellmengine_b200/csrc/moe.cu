@@ -16,56 +16,71 @@
 #include "common.cuh"
 #include <math_constants.h>
 
-#define MOE_ROUTE_THREADS 128
+#define MOE_ROUTE_THREADS 256
+#define MOE_ROUTE_TOKENS 4        // tokens a block takes: the router's matrix is read once for all of them
 
 template <typename TX>
 __global__ void moe_route_kernel(const TX* __restrict__ x, const float* __restrict__ wr, float* __restrict__ dense,
-                                 int32_t* __restrict__ ids, float* __restrict__ weights, int W, int E, int top,
-                                 int groups, int keep, float route_scale) {
+                                 int32_t* __restrict__ ids, float* __restrict__ weights, int num_tokens, int W, int E,
+                                 int top, int groups, int keep, float route_scale) {
     pdl_begin();
     extern __shared__ float smem[];
-    float* xs = smem;                    // [W]
-    float* score = xs + W;               // [E]
-    float* gscore = score + E;           // [groups]
-    int* allowed = reinterpret_cast<int*>(gscore + (groups > 0 ? groups : 1));      // [E]
-    const long long t = blockIdx.x;
+    const int G = groups > 0 ? groups : 1;
+    float* xs = smem;                                   // [TOKENS][W]
+    float* score = xs + MOE_ROUTE_TOKENS * W;           // [TOKENS][E]
+    float* gscore = score + MOE_ROUTE_TOKENS * E;       // [TOKENS][G]
+    int* allowed = reinterpret_cast<int*>(gscore + MOE_ROUTE_TOKENS * G);      // [TOKENS][E]
+    const long long t0 = static_cast<long long>(blockIdx.x) * MOE_ROUTE_TOKENS;
+    const int nt = static_cast<int>(min(static_cast<long long>(MOE_ROUTE_TOKENS), num_tokens - t0));
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    for (int i = tid; i < W; i += blockDim.x) xs[i] = to_f32(x[t * W + i]);
+    for (int i = tid; i < nt * W; i += blockDim.x) xs[i] = to_f32(x[t0 * W + i]);
     __syncthreads();
-    for (int e = warp; e < E; e += MOE_ROUTE_THREADS / 32) {
+    for (int e = warp; e < E; e += MOE_ROUTE_THREADS / 32) {       // a warp an expert: its row against the block's tokens
         const float* w = wr + static_cast<size_t>(e) * W;
-        float dot = 0.0f;
-        for (int i = lane; i < W; i += 32) dot += w[i] * xs[i];
-        dot = warp_sum(dot);
-        if (lane == 0) score[e] = 1.0f / (1.0f + expf(-dot));
+        float dot[MOE_ROUTE_TOKENS];
+#pragma unroll
+        for (int k = 0; k < MOE_ROUTE_TOKENS; ++k) dot[k] = 0.0f;
+        for (int i = lane; i < W; i += 32) {
+            const float wv = w[i];
+#pragma unroll
+            for (int k = 0; k < MOE_ROUTE_TOKENS; ++k) dot[k] += wv * xs[k * W + i];      // rows past nt hold stale data: never used
+        }
+#pragma unroll
+        for (int k = 0; k < MOE_ROUTE_TOKENS; ++k) {
+            const float d = warp_sum(dot[k]);
+            if (lane == 0 && k < nt) score[k * E + e] = 1.0f / (1.0f + expf(-d));
+        }
     }
     __syncthreads();
     const int per = groups > 0 ? E / groups : E;
-    if (groups > 0) {
-        for (int g = tid; g < groups; g += blockDim.x) {
-            float a = -1.0f, b = -1.0f;              // the two largest (scores are in (0, 1))
-            for (int j = 0; j < per; ++j) {
-                const float s = score[g * per + j];
-                if (s > a) { b = a; a = s; }
-                else if (s > b) b = s;
-            }
-            gscore[g] = per > 1 ? a + b : a;
+    for (int idx = tid; idx < nt * G && groups > 0; idx += blockDim.x) {
+        const int k = idx / G, g = idx - k * G;
+        float a = -1.0f, b = -1.0f;                  // the two largest (scores are in (0, 1))
+        for (int j = 0; j < per; ++j) {
+            const float sc = score[k * E + g * per + j];
+            if (sc > a) { b = a; a = sc; }
+            else if (sc > b) b = sc;
         }
+        gscore[idx] = per > 1 ? a + b : a;
     }
-    for (int e = tid; e < E; e += blockDim.x) {
-        allowed[e] = groups > 0 ? 0 : 1;
-        dense[t * E + e] = 0.0f;
+    for (int idx = tid; idx < nt * E; idx += blockDim.x) {
+        allowed[idx] = groups > 0 ? 0 : 1;
+        dense[t0 * E + idx] = 0.0f;
     }
     __syncthreads();
-    if (tid == 0) {
+    if (tid < nt) {                                  // one thread a token walks the choices (a few dozen steps)
+        const int k = tid;
+        const long long t = t0 + k;
+        float* sc = score + k * E;
+        int* ok = allowed + k * E;
         for (int n = 0; n < keep && groups > 0; ++n) {      // the best groups, ties to the lower index
             int best = -1;
             float bs = -CUDART_INF_F;
             for (int g = 0; g < groups; ++g)
-                if (gscore[g] > bs) { bs = gscore[g]; best = g; }
+                if (gscore[k * G + g] > bs) { bs = gscore[k * G + g]; best = g; }
             if (best < 0) break;
-            gscore[best] = -CUDART_INF_F;
-            for (int j = 0; j < per; ++j) allowed[best * per + j] = 1;
+            gscore[k * G + best] = -CUDART_INF_F;
+            for (int j = 0; j < per; ++j) ok[best * per + j] = 1;
         }
         float total = 0.0f;
         int chosen[64];
@@ -73,17 +88,17 @@ __global__ void moe_route_kernel(const TX* __restrict__ x, const float* __restri
             int best = -1;
             float bs = -CUDART_INF_F;
             for (int e = 0; e < E; ++e)
-                if (allowed[e] && score[e] > bs) { bs = score[e]; best = e; }
+                if (ok[e] && sc[e] > bs) { bs = sc[e]; best = e; }
             chosen[n] = best;
             if (best >= 0) {
-                allowed[best] = 0;
+                ok[best] = 0;
                 total += bs;
             }
         }
         const float inv = route_scale / (total + 1e-20f);
         for (int n = 0; n < top; ++n) {
             const int e = chosen[n];
-            const float w = e >= 0 ? score[e] * inv : 0.0f;
+            const float w = e >= 0 ? sc[e] * inv : 0.0f;
             if (e >= 0) dense[t * E + e] = w;
             if (ids) {
                 ids[t * top + n] = e;
@@ -99,17 +114,25 @@ extern "C" int llm_moe_route(const void* x, int x_dtype, const float* wr, float*
     if (num_tokens <= 0) return LLM_OK;
     if (W <= 0 || E <= 0 || top <= 0 || top > E || top > 64 || groups < 0) return LLM_REFUSED_SIZE;
     if (groups > 0 && (E % groups || keep <= 0 || keep > groups || keep * (E / groups) < top)) return LLM_REFUSED_SIZE;
-    const size_t smem = (static_cast<size_t>(W) + 2 * E + (groups > 0 ? groups : 1)) * sizeof(float);
-    if (smem > 48 * 1024) return LLM_REFUSED_SIZE;
+    const size_t smem = MOE_ROUTE_TOKENS * (static_cast<size_t>(W) + 2 * E + (groups > 0 ? groups : 1)) * sizeof(float);
+    if (smem > 200 * 1024) return LLM_REFUSED_SIZE;
     cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
-    if (x_dtype == LLM_DT_F32)
-        launch_pdl((moe_route_kernel<float>), dim3(num_tokens), dim3(MOE_ROUTE_THREADS), smem, s,
-                   static_cast<const float*>(x), wr, dense, ids, weights, W, E, top, groups, keep, route_scale);
-    else if (x_dtype == LLM_DT_BF16)
-        launch_pdl((moe_route_kernel<bf16>), dim3(num_tokens), dim3(MOE_ROUTE_THREADS), smem, s,
-                   static_cast<const bf16*>(x), wr, dense, ids, weights, W, E, top, groups, keep, route_scale);
-    else
-        return LLM_REFUSED_DTYPE;
+    const dim3 grid((num_tokens + MOE_ROUTE_TOKENS - 1) / MOE_ROUTE_TOKENS);
+#define LAUNCH(TX)                                                                                                  \
+    do {                                                                                                            \
+        auto kern = moe_route_kernel<TX>;                                                                           \
+        if (smem > 48 * 1024) {                                                                                     \
+            const cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,           \
+                                                       static_cast<int>(smem));                                     \
+            if (e != cudaSuccess) return static_cast<int>(e);                                                       \
+        }                                                                                                           \
+        launch_pdl(kern, grid, dim3(MOE_ROUTE_THREADS), smem, s, static_cast<const TX*>(x), wr, dense, ids, weights,  \
+                   num_tokens, W, E, top, groups, keep, route_scale);                                               \
+    } while (0)
+    if (x_dtype == LLM_DT_F32) LAUNCH(float);
+    else if (x_dtype == LLM_DT_BF16) LAUNCH(bf16);
+    else return LLM_REFUSED_DTYPE;
+#undef LAUNCH
     return launch_status();
 }
 
