@@ -677,25 +677,51 @@ def gubidra_bench(args, pk, measure) -> int:
     add(f"gla_step: {B} single tokens (like)",
         lambda: ops.gla_step(gp[:B], offs, la[:B], nv, 1e-5, D ** -0.5, 0.9, gout[:B], 0, state, slots, dq0, B, H, D, V),
         nbytes=2 * B * H * D * V * 4)
-    # attention with the distance table and a window, prompt portion and decode, beside the same kernel without them
+    # attention with the distance table, a gate per head and a window: the tensor-core kernel of prompt portions beside
+    # the same kernel without them and beside the tcgen05 kernel (what the closest model's prompt portions take); single
+    # tokens in the general kernel beside the split-key decode kernel
     pages = T // PAGE
-    keys = torch.randn(pages, kv, PAGE, d, device=dev).to(torch.bfloat16)
-    vals = torch.randn(pages, kv, PAGE, d, device=dev).to(torch.bfloat16)
+    cache = torch.randn(pages, 2, kv, PAGE, d, device=dev).to(torch.bfloat16)
     tbl = torch.arange(pages, device=dev, dtype=torch.int32).view(1, pages)
     ent = torch.zeros(T, device=dev, dtype=torch.int32)
     status = torch.zeros(2, dtype=torch.int32, device=dev)
     qa = torch.randn(T, heads * d, device=dev).to(torch.bfloat16)
     oa = torch.empty(T, heads * d, device=dev, dtype=torch.bfloat16)
     gate = torch.randn(T, heads, device=dev)
-    table = torch.randn(1024, heads, device=dev)
     window = 1024
+    table = torch.randn(window, heads, device=dev)
+    table_t = table.t().contiguous()
+    tiles = torch.tensor([(0, r) for r in range(0, T, ops.PREFILL_TILE_ROWS)], device=dev, dtype=torch.int32)
+    e_start, e_len = torch.zeros(1, device=dev, dtype=torch.int32), torch.full((1,), T, device=dev, dtype=torch.int32)
     walked = sum(min(p + 1, window) for p in range(T))
     attn_flops = 4.0 * heads * d * walked
-    for label, kw in (("attention, distance table + head gate (new)", dict(gate=gate, dist_bias=table, gate_per_head=True)),
-                      ("attention, the same kernel without them (like: the framework's general attention kernel)", {})):
-        sec = timed(lambda: ops.paged_attention_generic_kv(qa, keys, vals, pos, ent, slot0, tbl, heads, kv, d, d, PAGE, window, d ** -0.5,
-                                                           status, oa, 0, **kw), 3, 2, flush)
-        kernels[f"{label}: 2048-token portion, window 1024"] = {"us": round(sec * 1e6, 1), "tflops": round(attn_flops / sec / 1e12, 2)}
+    tensor_peak = pk.get("bf16_tflops", 1590.0) * 1e12
+
+    def attn(name, fn):
+        sec = timed(fn, 5, 3, flush)
+        kernels[name] = {"us": round(sec * 1e6, 1), "tflops": round(attn_flops / sec / 1e12, 1),
+                         "frac_of_bf16_peak": round(attn_flops / sec / tensor_peak, 4)}
+    common = (cache, tiles, tiles.shape[0], slot0, e_start, e_len, e_len, tbl, heads, kv, d, PAGE, window, d ** -0.5, status)
+    attn("prompt attention, distance table + head gate (new): 2048 tokens, window 1024",
+         lambda: ops.paged_attention_prefill_biased(qa, oa, 0, *common, dist_bias_t=table_t, head_gate=gate))
+    attn("prompt attention, the same mma.sync kernel without them (like)", lambda: ops.paged_attention_prefill(qa, oa, *common))
+    if ops.prefill_tcgen05_supported(d, PAGE):
+        attn("prompt attention, the tcgen05 kernel (like: what the closest model's prompt portions take)",
+             lambda: ops.paged_attention_prefill_tcgen05(qa, oa, *common))
+    Bd, ctx = 64, 1024
+    dpages = ctx // PAGE
+    dcache = torch.randn(Bd * dpages, 2, kv, PAGE, d, device=dev).to(torch.bfloat16)
+    dtbl = torch.arange(Bd * dpages, device=dev, dtype=torch.int32).view(Bd, dpages)
+    dpos = torch.full((Bd,), ctx - 1, device=dev, dtype=torch.int32)
+    dent = torch.arange(Bd, device=dev, dtype=torch.int32)
+    kv_bytes = Bd * ctx * 2 * kv * d * 2
+    add(f"decode attention, general kernel with distance table + head gate (new): {Bd} tokens, {ctx} keys each",
+        lambda: ops.paged_attention_generic_kv(qa[:Bd], dcache[:, 0], dcache[:, 1], dpos, dent, dent, dtbl, heads, kv, d, d, PAGE, window,
+                                               d ** -0.5, status, oa[:Bd], 0, gate=gate[:Bd], dist_bias=table, gate_per_head=True),
+        nbytes=kv_bytes)
+    add("decode attention, split-key kernel (like: what the closest model's single tokens take)",
+        lambda: ops.paged_attention_decode(qa[:Bd], oa[:Bd], dcache, None, Bd, dpos, dent, dent, dtbl, heads, kv, d, PAGE, window,
+                                           d ** -0.5, 2, status), nbytes=kv_bytes)
     # routed experts: router, activation, and the kernels that read only the chosen experts
     E, top, fe = 8, 2, ff // 2
     x = torch.randn(T, width, device=dev).to(torch.bfloat16)

@@ -63,7 +63,8 @@ __global__ void __launch_bounds__(AD_THREADS) paged_decode_attention_kernel(
     const int32_t* __restrict__ positions, const int32_t* __restrict__ token_entry,
     const int32_t* __restrict__ entry_slot, const int32_t* __restrict__ block_table, int table_stride,
     float* __restrict__ part_acc, float* __restrict__ part_ml, bf16* __restrict__ out, int nq, int nkv,
-    int page_size, int window, float scale_log2e, int num_pages, int num_splits, int32_t* __restrict__ status) {
+    int page_size, int window, float scale_log2e, int num_pages, int num_splits, int32_t* __restrict__ status,
+    const float* __restrict__ dist_bias, int dist_len) {
     pdl_begin();
     constexpr int CH = D / 8, KB = D / 16;
     extern __shared__ __align__(128) unsigned char smem_raw[];
@@ -177,9 +178,16 @@ __global__ void __launch_bounds__(AD_THREADS) paged_decode_attention_kernel(
         for (int nb = 0; nb < 2; ++nb)
 #pragma unroll
             for (int c = 0; c < 2; ++c) {
-                const bool vis = key0 + nb * 8 + (lane & 3) * 2 + c < k_end;
-                s[nb][c] = vis ? s[nb][c] * scale_log2e : -CUDART_INF_F;
-                s[nb][2 + c] = vis ? s[nb][2 + c] * scale_log2e : -CUDART_INF_F;
+                const int key = key0 + nb * 8 + (lane & 3) * 2 + c;
+                const bool vis = key < k_end;
+                float a0 = s[nb][c] * scale_log2e, a1 = s[nb][2 + c] * scale_log2e;
+                if (dist_bias && vis) {          // a learned bias by distance: a row of [heads, distances] per head, exp2 domain
+                    const int dist = min(max(pos - key, 0), dist_len - 1);
+                    a0 += __ldg(dist_bias + static_cast<size_t>(h0 + min(lane >> 2, G - 1)) * dist_len + dist);
+                    a1 += __ldg(dist_bias + static_cast<size_t>(h0 + min((lane >> 2) + 8, G - 1)) * dist_len + dist);
+                }
+                s[nb][c] = vis ? a0 : -CUDART_INF_F;
+                s[nb][2 + c] = vis ? a1 : -CUDART_INF_F;
                 mx0 = fmaxf(mx0, s[nb][c]);
                 mx1 = fmaxf(mx1, s[nb][2 + c]);
             }
@@ -299,7 +307,7 @@ static int launch_decode(const bf16* q, const bf16* cache, const int32_t* rows, 
                          const int32_t* token_entry, const int32_t* entry_slot, const int32_t* block_table,
                          int table_stride, float* part_acc, float* part_ml, bf16* out, int n_rows, int nq, int nkv,
                          int page_size, int window, float scale, int num_pages, int num_splits, int32_t* status,
-                         cudaStream_t s) {
+                         const float* dist_bias, int dist_len, cudaStream_t s) {
     const size_t smem = static_cast<size_t>(16 + 2 * AD_STAGES * AD_BN) * D * sizeof(bf16);
     auto kern = paged_decode_attention_kernel<D, AD_STAGES>;
     if (smem > 48 * 1024) {
@@ -319,14 +327,15 @@ static int launch_decode(const bf16* q, const bf16* cache, const int32_t* rows, 
         if (te != cudaSuccess) return static_cast<int>(te);                                                          \
         launch_pdl(tk, dim3(grid), dim3(AD_THREADS + 32), tsmem, s, *map, q, rows, positions, token_entry, entry_slot, block_table,      \
                                                 table_stride, part_acc, part_ml, out, nq, nkv, page_size, window,    \
-                                                scale * 1.4426950408889634f, num_pages, num_splits, status);         \
+                                                scale * 1.4426950408889634f, num_pages, num_splits, status,          \
+                                                dist_bias, dist_len);                                                \
     }
         TMA_GO(3)                                                   // three tiles in shared memory: one read, two in flight
 #undef TMA_GO
     } else {
         launch_pdl(kern, dim3(grid), dim3(AD_THREADS), smem, s, q, cache, rows, positions, token_entry, entry_slot, block_table, table_stride,
                                             part_acc, part_ml, out, nq, nkv, page_size, window,
-                                            scale * 1.4426950408889634f, num_pages, num_splits, status);
+                                            scale * 1.4426950408889634f, num_pages, num_splits, status, dist_bias, dist_len);
     }
     int rc = launch_status();
     if (rc != LLM_OK || num_splits == 1) return rc;
@@ -348,12 +357,15 @@ extern "C" long long llm_paged_decode_scratch_floats(int n_rows, int nq, int d, 
 
 // q, out: bfloat16 [T, nq*d]; cache: bfloat16 [pages, 2, nkv, page_size, d]; rows: int32 [n_rows] token
 // rows to attend for (null: rows 0..n_rows-1); scratch: float32, llm_paged_decode_scratch_floats long.
-extern "C" int llm_paged_attention_decode(
+// `dist_bias` float32 [nq, dist_len] (optional): a learned bias by distance in the exp2 domain (the table times
+// log2 e); row min(p - j, dist_len - 1) of a head joins the scaled score of the query at p and key j.
+extern "C" int llm_paged_attention_decode_biased(
     const void* q, void* out, const void* cache, const int32_t* rows, int n_rows, const int32_t* positions,
     const int32_t* token_entry, const int32_t* entry_slot, const int32_t* block_table, int table_stride, int nq,
     int nkv, int d, int page_size, int window, float scale, int num_pages, int num_splits, float* scratch,
-    int32_t* status, uintptr_t stream) {
+    int32_t* status, const float* dist_bias, int dist_len, uintptr_t stream) {
     if (n_rows <= 0) return LLM_OK;
+    if (dist_bias && dist_len <= 0) return LLM_REFUSED_SIZE;
     if (nq <= 0 || nkv <= 0 || nq % nkv != 0 || page_size <= 0 || num_splits < 1 || num_splits > 65535 ||
         nkv > 65535 || n_rows > 65535)
         return LLM_REFUSED_SIZE;
@@ -368,10 +380,20 @@ extern "C" int llm_paged_attention_decode(
     return launch_decode<DD, SS>(static_cast<const bf16*>(q), static_cast<const bf16*>(cache), rows, positions, \
                                  token_entry, entry_slot, block_table, table_stride, part_acc, part_ml,         \
                                  static_cast<bf16*>(out), n_rows, nq, nkv, page_size, window, scale, num_pages, \
-                                 num_splits, status, s)
+                                 num_splits, status, dist_bias, dist_len, s)
     if (d == 64) GO(64, 3);
     GO(128, 3);
 #undef GO
+}
+
+extern "C" int llm_paged_attention_decode(
+    const void* q, void* out, const void* cache, const int32_t* rows, int n_rows, const int32_t* positions,
+    const int32_t* token_entry, const int32_t* entry_slot, const int32_t* block_table, int table_stride, int nq,
+    int nkv, int d, int page_size, int window, float scale, int num_pages, int num_splits, float* scratch,
+    int32_t* status, uintptr_t stream) {
+    return llm_paged_attention_decode_biased(q, out, cache, rows, n_rows, positions, token_entry, entry_slot, block_table,
+                                             table_stride, nq, nkv, d, page_size, window, scale, num_pages, num_splits,
+                                             scratch, status, nullptr, 0, stream);
 }
 
 // ---- the entry point that allocates nothing (declared and explained in attention_decode_noalloc.h) ----

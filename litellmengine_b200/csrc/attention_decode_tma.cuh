@@ -70,7 +70,8 @@ __global__ void __launch_bounds__(AD_THREADS + 32) paged_decode_attention_tma_ke
     const int32_t* __restrict__ positions, const int32_t* __restrict__ token_entry,
     const int32_t* __restrict__ entry_slot, const int32_t* __restrict__ block_table, int table_stride,
     float* __restrict__ part_acc, float* __restrict__ part_ml, bf16* __restrict__ out, int nq, int nkv,
-    int page_size, int window, float scale_log2e, int num_pages, int num_splits, int32_t* __restrict__ status) {
+    int page_size, int window, float scale_log2e, int num_pages, int num_splits, int32_t* __restrict__ status,
+    const float* __restrict__ dist_bias, int dist_len) {
     // The wait for the kernel before this one (which writes q and this step's key and value row)
     // comes late: keys and values of earlier steps, the block table and the step's metadata are
     // read first, so the first tiles are already on their way when q arrives.
@@ -215,8 +216,14 @@ __global__ void __launch_bounds__(AD_THREADS + 32) paged_decode_attention_tma_ke
                 for (int c = 0; c < 2; ++c) {
                     const int key = key0 + nb * 8 + (lane & 3) * 2 + c;
                     const bool vis = key < k_end && key >= k_begin;
-                    s[nb][c] = vis ? s[nb][c] * scale_log2e : -CUDART_INF_F;
-                    s[nb][2 + c] = vis ? s[nb][2 + c] * scale_log2e : -CUDART_INF_F;
+                    float a0 = s[nb][c] * scale_log2e, a1 = s[nb][2 + c] * scale_log2e;
+                    if (dist_bias && vis) {      // a learned bias by distance: a row of [heads, distances] per head, exp2 domain
+                        const int dist = min(max(pos - key, 0), dist_len - 1);
+                        a0 += __ldg(dist_bias + static_cast<size_t>(h0 + min(lane >> 2, G - 1)) * dist_len + dist);
+                        a1 += __ldg(dist_bias + static_cast<size_t>(h0 + min((lane >> 2) + 8, G - 1)) * dist_len + dist);
+                    }
+                    s[nb][c] = vis ? a0 : -CUDART_INF_F;
+                    s[nb][2 + c] = vis ? a1 : -CUDART_INF_F;
                     mx0 = fmaxf(mx0, s[nb][c]);
                     mx1 = fmaxf(mx1, s[nb][2 + c]);
                 }

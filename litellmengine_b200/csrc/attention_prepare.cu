@@ -206,7 +206,8 @@ extern "C" int llm_attention_prepare(
 template <typename T>
 __global__ void gate_mul_kernel(const T* __restrict__ a, const float* __restrict__ g, long long g_stride, int g_off,
                                 T* __restrict__ out, long long out_stride, int out_off, int width, int gate_kind,
-                                float scale, int vec) {
+                                float scale, int vec, int per_head) {
+    // per_head > 0: one gate value per head of `per_head` channels (gate column g_off + channel / per_head)
     pdl_begin();
     const size_t t = blockIdx.y;
     if (vec) {                                       // 16-byte accesses, 8 elements a thread a trip
@@ -214,7 +215,13 @@ __global__ void gate_mul_kernel(const T* __restrict__ a, const float* __restrict
             float x[8], z[8];
             load8(a + t * width + i, x);
             if (gate_kind != 0) {
-                load8(g + t * g_stride + g_off + i, z);
+                if (per_head > 0) {                  // eight neighbours share a head (per_head is a multiple of 8 here)
+                    const float one = g[t * g_stride + g_off + i / per_head];
+#pragma unroll
+                    for (int u = 0; u < 8; ++u) z[u] = one;
+                } else {
+                    load8(g + t * g_stride + g_off + i, z);
+                }
 #pragma unroll
                 for (int u = 0; u < 8; ++u) {
                     const float s = 1.0f / (1.0f + expf(-z[u]));
@@ -230,7 +237,7 @@ __global__ void gate_mul_kernel(const T* __restrict__ a, const float* __restrict
     for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < width; i += gridDim.x * blockDim.x) {
         float gate = 1.0f;
         if (gate_kind != 0) {
-            const float z = g[t * g_stride + g_off + i];
+            const float z = g[t * g_stride + g_off + (per_head > 0 ? i / per_head : i)];
             const float s = 1.0f / (1.0f + expf(-z));
             gate = gate_kind == 2 ? z * s : s;
         }
@@ -240,23 +247,25 @@ __global__ void gate_mul_kernel(const T* __restrict__ a, const float* __restrict
 
 extern "C" int llm_gate_mul(const void* a, int dtype, const float* g, long long g_stride, int g_off, void* out,
                             long long out_stride, int out_off, int num_tokens, int width, int gate_kind, float scale,
-                            uintptr_t stream) {
+                            int per_head, uintptr_t stream) {
     if (num_tokens <= 0) return LLM_OK;
     if (width <= 0 || num_tokens > 65535 || gate_kind < 0 || gate_kind > 2 || (gate_kind && !g)) return LLM_REFUSED_SIZE;
     const int threads = 256;
     const int esz = dtype == LLM_DT_F32 ? 4 : 2;
-    const int vec = width % 8 == 0 && out_stride % 8 == 0 && out_off % 8 == 0 && aligned16(a) && aligned16(out) &&
-                    (!g || (aligned16(g) && g_stride % 4 == 0 && g_off % 4 == 0)) && esz > 0;
+    if (per_head < 0) return LLM_REFUSED_SIZE;
+    // sixteen-byte accesses: per channel the gate row is read in eights too; per head eight neighbours share one value
+    const int vec = width % 8 == 0 && out_stride % 8 == 0 && out_off % 8 == 0 && aligned16(a) && aligned16(out) && esz > 0 &&
+                    (per_head > 0 ? per_head % 8 == 0 : (!g || (aligned16(g) && g_stride % 4 == 0 && g_off % 4 == 0)));
     const int per_row = vec ? width / 8 : width;
     const int bx = (per_row + threads - 1) / threads;
     const dim3 grid(bx < 64 ? bx : 64, num_tokens);
     cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
     if (dtype == LLM_DT_F32)
         launch_pdl((gate_mul_kernel<float>), grid, dim3(threads), 0, s, static_cast<const float*>(a), g, g_stride, g_off,
-                   static_cast<float*>(out), out_stride, out_off, width, gate_kind, scale, vec);
+                   static_cast<float*>(out), out_stride, out_off, width, gate_kind, scale, vec, per_head);
     else if (dtype == LLM_DT_BF16)
         launch_pdl((gate_mul_kernel<bf16>), grid, dim3(threads), 0, s, static_cast<const bf16*>(a), g, g_stride, g_off,
-                   static_cast<bf16*>(out), out_stride, out_off, width, gate_kind, scale, vec);
+                   static_cast<bf16*>(out), out_stride, out_off, width, gate_kind, scale, vec, per_head);
     else
         return LLM_REFUSED_DTYPE;
     return launch_status();

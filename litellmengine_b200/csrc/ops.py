@@ -471,9 +471,10 @@ def attention_prepare(proj: torch.Tensor, q_off: int, k_off: int, v_off: int, bi
 
 
 def gate_mul(a: torch.Tensor, gate: Optional[torch.Tensor], gate_off: int, out: torch.Tensor, out_off: int,
-             kind: Optional[str], scale: float = 1.0) -> None:
+             kind: Optional[str], scale: float = 1.0, per_head: int = 0) -> None:
     """out[:, out_off : out_off + w] = a * gate_fn(gate[:, gate_off : gate_off + w]) * scale for a contiguous
-    a [T, w]; gate is float32; `kind` 'sigmoid', 'silu' or None (no gate: scale and place only)."""
+    a [T, w]; gate is float32; `kind` 'sigmoid', 'silu' or None (no gate: scale and place only).  `per_head` > 0:
+    one gate value per head of that many channels (gate[:, gate_off + channel // per_head])."""
     _dev(a)
     T, w = a.shape
     if kind is None:
@@ -481,9 +482,10 @@ def gate_mul(a: torch.Tensor, gate: Optional[torch.Tensor], gate_off: int, out: 
     if (gate is not None and (gate.dtype != torch.float32 or gate.stride(1) != 1)) or out.stride(1) != 1 or out.dtype != a.dtype:
         raise KernelError("gate must be float32, out of a's dtype, both with unit stride along rows")
     f = _fn("attention_prepare", "llm_gate_mul",
-            [c_void_p, c_int, c_void_p, c_longlong, c_int, c_void_p, c_longlong, c_int, c_int, c_int, c_int, c_float, c_void_p])
+            [c_void_p, c_int, c_void_p, c_longlong, c_int, c_void_p, c_longlong, c_int, c_int, c_int, c_int, c_float, c_int,
+             c_void_p])
     _check(f(_ptr(a), _dt(a), _ptr(gate), gate.stride(0) if gate is not None else 0, gate_off, _ptr(out), out.stride(0),
-             out_off, T, w, {None: 0, "sigmoid": 1, "silu": 2}[kind], float(scale), _stream()), "gate_mul")
+             out_off, T, w, {None: 0, "sigmoid": 1, "silu": 2}[kind], float(scale), int(per_head), _stream()), "gate_mul")
 
 
 def paged_attention_generic_kv(q: torch.Tensor, keys: torch.Tensor, values: torch.Tensor, positions, token_entry,
@@ -894,10 +896,13 @@ def decode_scratch(device, floats: int) -> Optional[torch.Tensor]:
 def paged_attention_decode(q: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, rows: Optional[torch.Tensor],
                            n_rows: int, positions, token_entry, entry_slot, block_table: torch.Tensor, nq: int,
                            nkv: int, d: int, page_size: int, window: Optional[int], scale: float, num_splits: int,
-                           status: torch.Tensor) -> torch.Tensor:
+                           status: torch.Tensor, dist_bias_t: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Attention for single decoded tokens (rows of q named by `rows`, or rows 0..n_rows-1), written
-    into the same rows of `out`.  bfloat16 only."""
-    _dev(q, out, cache, rows, positions, token_entry, entry_slot, block_table, status)
+    into the same rows of `out`.  bfloat16 only.  `dist_bias_t` float32 [nq, distances]: a bias by distance TIMES
+    log2(e); row min(p - j, distances - 1) of a head joins the scaled score of the query at p and key j."""
+    _dev(q, out, cache, rows, positions, token_entry, entry_slot, block_table, status, dist_bias_t)
+    if dist_bias_t is not None and (dist_bias_t.dtype != torch.float32 or dist_bias_t.dim() != 2 or dist_bias_t.shape[0] != nq):
+        raise KernelError("dist_bias_t must be float32 [heads, distances]")
     if q.dtype != torch.bfloat16 or cache.dtype != torch.bfloat16 or out.dtype != torch.bfloat16:
         raise KernelError("the decode attention kernel is bfloat16 only")
     if q.shape[1] != nq * d or tuple(cache.shape[1:]) != (2, nkv, page_size, d):
@@ -905,13 +910,13 @@ def paged_attention_decode(q: torch.Tensor, out: torch.Tensor, cache: torch.Tens
     need = _fn("attention_decode", "llm_paged_decode_scratch_floats", [c_int, c_int, c_int, c_int],
                restype=c_longlong)(n_rows, nq, d, num_splits)
     scratch = decode_scratch(q.device, int(need))
-    f = _fn("attention_decode", "llm_paged_attention_decode",
+    f = _fn("attention_decode", "llm_paged_attention_decode_biased",
             [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
-             c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p, c_void_p, c_void_p])
+             c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p])
     _check(f(_ptr(q), _ptr(out), _ptr(cache), _ptr(rows), n_rows, _ptr(positions), _ptr(token_entry),
              _ptr(entry_slot), _ptr(block_table), block_table.shape[1], nq, nkv, d, page_size,
              int(window) if window else 0, float(scale), cache.shape[0], num_splits, _ptr(scratch), _ptr(status),
-             _stream()), "paged_attention_decode")
+             _ptr(dist_bias_t), dist_bias_t.shape[1] if dist_bias_t is not None else 0, _stream()), "paged_attention_decode")
     if num_splits > 1:
         global launch_count
         launch_count += 1                         # the merge kernel

@@ -51,7 +51,8 @@ __device__ __forceinline__ void stream_store4(bf16* p, float a, float b, float c
     *reinterpret_cast<uint2*>(p) = raw;
 }
 
-template <typename TY, typename TO>
+// SM: the most streams this instantiation holds in registers (1, 2, 4 or 8).
+template <typename TY, typename TO, int SM>
 __global__ void stream_norm_kernel(float* __restrict__ streams, long long stream_stride, long long read_stride, int S,
                                    const TY* __restrict__ y, int y_parts, long long y_part_stride,
                                    const float* __restrict__ mix, const float* __restrict__ outw,
@@ -77,9 +78,9 @@ __global__ void stream_norm_kernel(float* __restrict__ streams, long long stream
     // four neighbouring columns a thread and trip when the rows allow sixteen-byte accesses, else one
     const int step = vec ? 4 : 1;
     for (int h = threadIdx.x * step; h < hidden; h += blockDim.x * step) {
-        float x[ST_MAX][4];
+        float x[SM][4];
 #pragma unroll
-        for (int s = 0; s < ST_MAX; ++s)
+        for (int s = 0; s < SM; ++s)
             if (s < S) {
                 if (vec) {
                     const float4 v = *reinterpret_cast<const float4*>(xr + s * read_stride + h);
@@ -98,11 +99,11 @@ __global__ void stream_norm_kernel(float* __restrict__ streams, long long stream
                 for (int c = 0; c < 4; ++c) yv[c] += one[c];
             }
 #pragma unroll
-            for (int t = 0; t < ST_MAX; ++t)
+            for (int t = 0; t < SM; ++t)
                 if (t < S) {
                     float nt[4] = {0.0f, 0.0f, 0.0f, 0.0f};
 #pragma unroll
-                    for (int s = 0; s < ST_MAX; ++s)
+                    for (int s = 0; s < SM; ++s)
                         if (s < S) {
 #pragma unroll
                             for (int c = 0; c < 4; ++c) nt[c] += coef[s * S + t] * x[s][c];
@@ -119,7 +120,7 @@ __global__ void stream_norm_kernel(float* __restrict__ streams, long long stream
                 }
         } else {
 #pragma unroll
-            for (int t = 0; t < ST_MAX; ++t)
+            for (int t = 0; t < SM; ++t)
                 if (t < S) {
 #pragma unroll
                     for (int c = 0; c < 4; ++c) acc[c] += coef[S * S + S + t] * x[t][c];
@@ -175,13 +176,13 @@ extern "C" int llm_stream_norm(float* streams, long long stream_stride, long lon
     const size_t smem = (static_cast<size_t>((hidden + 7) & ~7) + 33 + S * S + 2 * S) * sizeof(float);
     if (smem > 200 * 1024) return LLM_REFUSED_SIZE;
     cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
-    const int threads = hidden >= 4096 ? 512 : (hidden >= 1024 ? 256 : 128);
+    const int threads = hidden >= 1024 ? 256 : 128;
     if (y_parts < 1) y_parts = 1;
     const int vec = hidden % 4 == 0 && aligned16(streams) && stream_stride % 4 == 0 && read_stride % 4 == 0 &&
                     (!y || (aligned16(y) && y_part_stride % 4 == 0)) && (!w || aligned16(w)) && (!out || aligned16(out));
-#define LAUNCH(TY, TO)                                                                                              \
+#define LAUNCH_S(TY, TO, SMAX)                                                                                      \
     do {                                                                                                            \
-        auto kern = stream_norm_kernel<TY, TO>;                                                                     \
+        auto kern = stream_norm_kernel<TY, TO, SMAX>;                                                               \
         if (smem > 48 * 1024) {                                                                                     \
             const cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,           \
                                                        static_cast<int>(smem));                                     \
@@ -191,6 +192,13 @@ extern "C" int llm_stream_norm(float* streams, long long stream_stride, long lon
                    static_cast<const TY*>(y), y_parts, y_part_stride, mix, outw, inw, w, eps, center,               \
                    static_cast<TO*>(out), rows, hidden, write_back, vec);                                           \
     } while (0)
+#define LAUNCH(TY, TO)                                                                                              \
+    do {                                                                                                            \
+        if (S == 1) LAUNCH_S(TY, TO, 1);                                                                            \
+        else if (S == 2) LAUNCH_S(TY, TO, 2);                                                                       \
+        else if (S <= 4) LAUNCH_S(TY, TO, 4);                                                                       \
+        else LAUNCH_S(TY, TO, 8);                                                                                   \
+    } while (0)
     if (!y) y_dtype = LLM_DT_F32;
     if (!out) out_dtype = LLM_DT_F32;
     if (y_dtype == LLM_DT_F32 && out_dtype == LLM_DT_F32) LAUNCH(float, float);
@@ -199,5 +207,6 @@ extern "C" int llm_stream_norm(float* streams, long long stream_stride, long lon
     else if (y_dtype == LLM_DT_BF16 && out_dtype == LLM_DT_BF16) LAUNCH(bf16, bf16);
     else return LLM_REFUSED_DTYPE;
 #undef LAUNCH
+#undef LAUNCH_S
     return launch_status();
 }

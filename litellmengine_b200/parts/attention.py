@@ -281,6 +281,7 @@ class GatedAttentionMixer(BranchMixer):
         self._tuned_prompt = (not self._tuned and compute_dtype == torch.bfloat16 and self.dv == self.d
                               and self.device.type == "cuda" and (self.gate_per_head or not spec.output_gate)
                               and ops.prefill_attention_supported(self.d))
+        self._tuned_decode = self._tuned_prompt and ops.fast_attention_supported(self.d, self.nq // self.nkv)
         self.dist_table_t = None
 
     def parameters(self) -> Dict[str, ParamSpec]:
@@ -334,12 +335,21 @@ class GatedAttentionMixer(BranchMixer):
 
     @property
     def graph_variant_group(self):
-        return ("attention", self.nkv) if self._tuned else ("gated_attention",)
+        return ("attention", self.nkv) if self._tuned else ("gated_attention", self.nkv, self.spec.window)
+
+    def _decode_reach(self, batch) -> int:
+        """The most keys a single token of this step walks: the longest cached length, or the window."""
+        return min(batch.max_kv_len, self.spec.window) if self.spec.window else batch.max_kv_len
 
     def graph_variant(self, batch, padded: bool) -> int:
-        if not self._tuned:
+        if self._tuned:
+            return AttentionMixer.graph_variant(self, batch, padded)
+        if not self._tuned_decode:
             return 0
-        return AttentionMixer.graph_variant(self, batch, padded)
+        work = batch.preludes.get(AttentionWork.name)       # the decode kernel's key splits, as the step will choose them
+        n_dec = 0 if work is None else (work.padded_rows.shape[0] if padded else work.num_decode)
+        n_tiles = 0 if work is None else (work.padded_tiles.shape[0] if padded else work.num_prefill_tiles)
+        return decode_key_splits(self.device, n_dec, self.nkv, self._decode_reach(batch)) if n_dec and not n_tiles else 0
 
     def mix(self, proj, col0, ctx, out, out_col0, out_scale):
         b, s = ctx.batch, self.spec
@@ -356,16 +366,30 @@ class GatedAttentionMixer(BranchMixer):
             return
         work = b.preludes.get(AttentionWork.name) if self._tuned_prompt and ctx.cache is not None else None
         padded = getattr(b, "any_division", False)
-        if work is not None and (padded or work.num_prefill_tiles):
-            # prompt portions on the tensor cores, the step's single tokens (if any) in the general kernel
+        if work is not None:
+            # prompt portions on the tensor cores (bias added to the scores, gate and scale as the kernel stores);
+            # single tokens in the split-key decode kernel where it takes the group (bias likewise, the gate in a
+            # small kernel after it), else in the general kernel by the list of their rows
             n_tiles = work.padded_tiles.shape[0] if padded else work.num_prefill_tiles
-            ops.paged_attention_prefill_biased(
-                q, out, out_col0, ctx.cache, work.padded_tiles if padded else work.prefill_tiles, n_tiles, b.entry_slot,
-                b.entry_q_start, b.entry_q_len, b.entry_kv_len, ctx.block_table, self.nq, self.nkv, self.d, ctx.page_size,
-                s.window, self.scale, ctx.status, dist_bias_t=self.dist_table_t, head_gate=proj if s.output_gate else None,
-                gate_off=col0 + self.g_off, out_scale=out_scale)
-            rows = work.padded_rows if padded else (work.decode_rows if work.num_decode else None)
-            if rows is None:
+            n_dec = work.padded_rows.shape[0] if padded else work.num_decode
+            gate = proj if s.output_gate else None
+            if n_tiles:
+                ops.paged_attention_prefill_biased(
+                    q, out, out_col0, ctx.cache, work.padded_tiles if padded else work.prefill_tiles, n_tiles, b.entry_slot,
+                    b.entry_q_start, b.entry_q_len, b.entry_kv_len, ctx.block_table, self.nq, self.nkv, self.d, ctx.page_size,
+                    s.window, self.scale, ctx.status, dist_bias_t=self.dist_table_t, head_gate=gate,
+                    gate_off=col0 + self.g_off, out_scale=out_scale)
+            if not n_dec:
+                return
+            rows = work.padded_rows if padded else (None if n_dec == b.num_tokens else work.decode_rows)
+            if self._tuned_decode and not n_tiles:
+                a = torch.empty_like(q)
+                splits = decode_key_splits(q.device, n_dec, self.nkv, self._decode_reach(b))
+                ops.paged_attention_decode(q, a, ctx.cache, rows, n_dec, b.positions, b.token_entry, b.entry_slot,
+                                           ctx.block_table, self.nq, self.nkv, self.d, ctx.page_size, s.window, self.scale, splits,
+                                           ctx.status, dist_bias_t=self.dist_table_t)
+                ops.gate_mul(a, gate, col0 + self.g_off, out, out_col0, s.output_gate, out_scale,
+                             per_head=self.dv if self.gate_per_head else 0)
                 return
         else:
             rows = None

@@ -578,3 +578,14 @@ def test_tensor_core_prompt_attention_with_distance_bias_and_head_gate(d, window
     got = out[:, 16:].double().cpu().view(T, H, d)
     assert (got - ref).abs().max() < 0.06
     assert float(out[:, :16].abs().max()) == 0.0
+    # single tokens in the split-key decode kernel (the table joins its scores; the gate per head in the kernel after it)
+    for splits in (1, 3):
+        a = torch.zeros(T, H * d, dtype=torch.bfloat16, device=DEV)
+        picked = [T - 1, 5, 150]
+        ops.paged_attention_decode(qd, a, cache, _i32(picked + [-1]), 4, _i32(list(range(past, N))), _i32([0] * T), _i32([1]),
+                                   block_table, H, G, d, page, window, scale, splits, status, dist_bias_t=table_t)
+        out2 = torch.zeros(T, H * d + 16, dtype=torch.bfloat16, device=DEV)
+        ops.gate_mul(a, gate_buf, 5, out2, 16, "sigmoid", 1.0, per_head=d)
+        assert status.tolist() == [0, 0]
+        got2 = out2[:, 16:].double().cpu().view(T, H, d)
+        assert (got2[picked] - ref[picked]).abs().max() < 0.06, splits
