@@ -715,7 +715,16 @@ def gubidra_bench(args, pk, measure) -> int:
     dpos = torch.full((Bd,), ctx - 1, device=dev, dtype=torch.int32)
     dent = torch.arange(Bd, device=dev, dtype=torch.int32)
     kv_bytes = Bd * ctx * 2 * kv * d * 2
-    add(f"decode attention, general kernel with distance table + head gate (new): {Bd} tokens, {ctx} keys each",
+    table_t2 = (table.t() * 1.4426950408889634).contiguous()
+    a_dec = torch.empty(Bd, heads * d, device=dev, dtype=torch.bfloat16)
+
+    def biased_decode():
+        ops.paged_attention_decode(qa[:Bd], a_dec, dcache, None, Bd, dpos, dent, dent, dtbl, heads, kv, d, PAGE, window, d ** -0.5, 2,
+                                   status, dist_bias_t=table_t2)
+        ops.gate_mul(a_dec, gate[:Bd], 0, oa[:Bd], 0, "sigmoid", 1.0, per_head=d)
+    add(f"decode attention, split-key kernel with the distance table, then the gate per head (new): {Bd} tokens, {ctx} keys each",
+        biased_decode, nbytes=kv_bytes)
+    add(f"decode attention, general kernel with distance table + head gate (new; the 32-bit mode and odd shapes): {Bd} tokens, {ctx} keys each",
         lambda: ops.paged_attention_generic_kv(qa[:Bd], dcache[:, 0], dcache[:, 1], dpos, dent, dent, dtbl, heads, kv, d, d, PAGE, window,
                                                d ** -0.5, status, oa[:Bd], 0, gate=gate[:Bd], dist_bias=table, gate_per_head=True),
         nbytes=kv_bytes)

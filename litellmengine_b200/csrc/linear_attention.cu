@@ -797,7 +797,8 @@ extern "C" int llm_gla_chain(float* state, float* scratch_s, const float* scratc
 // maximum m' = max(f + m, i) (m from the head's state, written back at the end), and per token
 //     keep = exp(f + m - m'),   put = exp(i - m'),   floor = exp(-m')
 // into three float32 [T, H] arrays (`gates` [3, T, H]).  Tokens are taken 128 at a time: every thread makes
-// one token's log gates, one thread walks the maxima, every thread stores.
+// one token's log gates, one thread walks the maxima (an add and a max a token), every thread makes its token's
+// exponentials and stores.
 #define RG_TOKENS 128
 __global__ void recur_gates_kernel(const float* __restrict__ proj, long long stride, int i_off, int f_off,
                                    const float* __restrict__ i_bias, const float* __restrict__ f_bias, float cap,
@@ -806,7 +807,7 @@ __global__ void recur_gates_kernel(const float* __restrict__ proj, long long str
                                    const int32_t* __restrict__ entry_slot, const int32_t* __restrict__ entry_q_start,
                                    const int32_t* __restrict__ entry_q_len, int H) {
     pdl_begin();
-    __shared__ float ig[RG_TOKENS], fg[RG_TOKENS], fl[RG_TOKENS];
+    __shared__ float ig[RG_TOKENS], fg[RG_TOKENS], fl[RG_TOKENS], mx[RG_TOKENS];
     __shared__ float carry;
     const int entry = blockIdx.x, h = blockIdx.y, tid = threadIdx.x;
     const long long row0 = entry_q_start[entry];
@@ -822,23 +823,23 @@ __global__ void recur_gates_kernel(const float* __restrict__ proj, long long str
             recur_log_gates(pr[i_off + h] + bi, pr[f_off + h] + bf, cap, ig[tid], fg[tid]);
         }
         __syncthreads();
-        if (tid == 0) {
+        if (tid == 0) {                                    // the chain itself is an add and a max a token
             float m = carry;
             for (int t = 0; t < nb; ++t) {
                 const float m_new = fmaxf(fg[t] + m, ig[t]);
-                fg[t] = expf(fg[t] + m - m_new);           // keep
-                ig[t] = expf(ig[t] - m_new);               // put
-                fl[t] = expf(-m_new);
+                fl[t] = m;                                 // the maximum that entered the token
+                mx[t] = m_new;
                 m = m_new;
             }
             carry = m;
         }
         __syncthreads();
-        if (tid < nb) {
+        if (tid < nb) {                                    // the exponentials, a token a thread
             const long long at = (row0 + done + tid) * H + h;
-            gates[at] = fg[tid];
-            gates[num_tokens * H + at] = ig[tid];
-            gates[2 * num_tokens * H + at] = fl[tid];
+            const float m_old = fl[tid], m_new = mx[tid];
+            gates[at] = expf(fg[tid] + m_old - m_new);                        // keep
+            gates[num_tokens * H + at] = expf(ig[tid] - m_new);               // put
+            gates[2 * num_tokens * H + at] = expf(-m_new);                    // floor
         }
     }
     __syncthreads();

@@ -22,7 +22,7 @@
 template <typename TX>
 __global__ void moe_route_kernel(const TX* __restrict__ x, const float* __restrict__ wr, float* __restrict__ dense,
                                  int32_t* __restrict__ ids, float* __restrict__ weights, int num_tokens, int W, int E,
-                                 int top, int groups, int keep, float route_scale) {
+                                 int top, int groups, int keep, float route_scale, int vec) {
     pdl_begin();
     extern __shared__ float smem[];
     const int G = groups > 0 ? groups : 1;
@@ -33,17 +33,38 @@ __global__ void moe_route_kernel(const TX* __restrict__ x, const float* __restri
     const long long t0 = static_cast<long long>(blockIdx.x) * MOE_ROUTE_TOKENS;
     const int nt = static_cast<int>(min(static_cast<long long>(MOE_ROUTE_TOKENS), num_tokens - t0));
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    for (int i = tid; i < nt * W; i += blockDim.x) xs[i] = to_f32(x[t0 * W + i]);
+    if (vec) {                                          // sixteen-byte loads of the tokens' rows
+        for (int i = tid * 8; i < nt * W; i += blockDim.x * 8) {
+            float v[8];
+            load8(x + t0 * W + i, v);
+#pragma unroll
+            for (int u = 0; u < 8; ++u) xs[i + u] = v[u];
+        }
+    } else {
+        for (int i = tid; i < nt * W; i += blockDim.x) xs[i] = to_f32(x[t0 * W + i]);
+    }
     __syncthreads();
     for (int e = warp; e < E; e += MOE_ROUTE_THREADS / 32) {       // a warp an expert: its row against the block's tokens
         const float* w = wr + static_cast<size_t>(e) * W;
         float dot[MOE_ROUTE_TOKENS];
 #pragma unroll
         for (int k = 0; k < MOE_ROUTE_TOKENS; ++k) dot[k] = 0.0f;
-        for (int i = lane; i < W; i += 32) {
-            const float wv = w[i];
+        if (vec) {                                      // sixteen bytes of the row a lane and trip, four trips in flight
+#pragma unroll 4
+            for (int i = lane * 4; i < W; i += 128) {
+                const float4 wv = *reinterpret_cast<const float4*>(w + i);
 #pragma unroll
-            for (int k = 0; k < MOE_ROUTE_TOKENS; ++k) dot[k] += wv * xs[k * W + i];      // rows past nt hold stale data: never used
+                for (int k = 0; k < MOE_ROUTE_TOKENS; ++k) {      // rows past nt hold stale data: never used
+                    const float4 xv = *reinterpret_cast<const float4*>(xs + k * W + i);
+                    dot[k] += wv.x * xv.x + wv.y * xv.y + wv.z * xv.z + wv.w * xv.w;
+                }
+            }
+        } else {
+            for (int i = lane; i < W; i += 32) {
+                const float wv = w[i];
+#pragma unroll
+                for (int k = 0; k < MOE_ROUTE_TOKENS; ++k) dot[k] += wv * xs[k * W + i];
+            }
         }
 #pragma unroll
         for (int k = 0; k < MOE_ROUTE_TOKENS; ++k) {
@@ -118,6 +139,7 @@ extern "C" int llm_moe_route(const void* x, int x_dtype, const float* wr, float*
     if (smem > 200 * 1024) return LLM_REFUSED_SIZE;
     cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
     const dim3 grid((num_tokens + MOE_ROUTE_TOKENS - 1) / MOE_ROUTE_TOKENS);
+    const int vec = W % 8 == 0 && aligned16(x) && aligned16(wr);
 #define LAUNCH(TX)                                                                                                  \
     do {                                                                                                            \
         auto kern = moe_route_kernel<TX>;                                                                           \
@@ -127,7 +149,7 @@ extern "C" int llm_moe_route(const void* x, int x_dtype, const float* wr, float*
             if (e != cudaSuccess) return static_cast<int>(e);                                                       \
         }                                                                                                           \
         launch_pdl(kern, grid, dim3(MOE_ROUTE_THREADS), smem, s, static_cast<const TX*>(x), wr, dense, ids, weights,  \
-                   num_tokens, W, E, top, groups, keep, route_scale);                                               \
+                   num_tokens, W, E, top, groups, keep, route_scale, vec);                                          \
     } while (0)
     if (x_dtype == LLM_DT_F32) LAUNCH(float);
     else if (x_dtype == LLM_DT_BF16) LAUNCH(bf16);

@@ -176,7 +176,10 @@ extern "C" int llm_stream_norm(float* streams, long long stream_stride, long lon
     const size_t smem = (static_cast<size_t>((hidden + 7) & ~7) + 33 + S * S + 2 * S) * sizeof(float);
     if (smem > 200 * 1024) return LLM_REFUSED_SIZE;
     cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
-    const int threads = hidden >= 1024 ? 256 : 128;
+    // few rows (a decode step): more threads a row, up to 512 (what the widest instantiation's registers allow),
+    // so that a row takes fewer trips
+    int threads = hidden >= 1024 ? 256 : 128;
+    if (num_rows <= 256 && hidden > 4 * threads) threads = hidden / 4 >= 512 ? 512 : ((hidden / 4 + 31) / 32) * 32;
     if (y_parts < 1) y_parts = 1;
     const int vec = hidden % 4 == 0 && aligned16(streams) && stream_stride % 4 == 0 && read_stride % 4 == 0 &&
                     (!y || (aligned16(y) && y_part_stride % 4 == 0)) && (!w || aligned16(w)) && (!out || aligned16(out));
