@@ -22,12 +22,14 @@ class StreamConnection:
 
     def parameters(self) -> Dict[str, ParamSpec]:
         S = self.streams
-        return {"in": ParamSpec((S,), role="scale", init=("one_plus_normal", 0.1)),
-                "out": ParamSpec((S,), role="scale", init=("one_plus_normal", 0.1)),
-                "mix": ParamSpec((S, S), role="scale", init=("normal", 0.5))}
+        lone = S == 1          # one stream may come without connection tensors: it is then the plain residual stream
+        return {"in": ParamSpec((S,), role="scale", init=("one_plus_normal", 0.1), optional=lone),
+                "out": ParamSpec((S,), role="scale", init=("one_plus_normal", 0.1), optional=lone),
+                "mix": ParamSpec((S, S), role="scale", init=("normal", 0.5), optional=lone)}
 
     def load(self, tensors: Dict[str, torch.Tensor]) -> None:
-        self.inp, self.out, self.mix = (tensors[k].contiguous() for k in ("in", "out", "mix"))
+        # an absent tensor stays None, which the streams' kernel reads as ones (in, out) or the identity (mix)
+        self.inp, self.out, self.mix = (tensors[k].contiguous() if k in tensors else None for k in ("in", "out", "mix"))
 
 
 class PendingUpdate:

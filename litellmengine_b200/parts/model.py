@@ -68,9 +68,12 @@ class Model:
             ops.begin_model(sum(2 * ps.shape[0] * ps.shape[1] for n, ps in params.items()
                                 if len(ps.shape) == 2 and n not in aliased), self.device)
         get = lambda n: fetch_tensor(source, n, params[n], self.dtype, self.device)
+        have = set(source.names())
         self.embedding = get(p.embedding_name).contiguous()
         for spec, block in zip(p.blocks, self.blocks):
-            block.load({n: get(f"{spec.weight_prefix}.{n}") for n in block.parameters()})
+            # a tensor that may be absent and is: the part is handed nothing for it
+            block.load({n: get(f"{spec.weight_prefix}.{n}") for n, ps in block.parameters().items()
+                        if not (ps.optional and f"{spec.weight_prefix}.{n}" not in have)})
         self.final_norm.load({next(iter(self.final_norm.parameters())): get(p.final_norm_name)})
         self.output = self.embedding if p.output_name in aliased else get(p.output_name).contiguous()
         ops.prepare_streaming(self.output)          # a tiled copy of the output head for decode steps

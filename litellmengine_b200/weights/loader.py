@@ -57,6 +57,7 @@ class ParamSpec:
     'index': an integer table; held as int32.
     init: ('normal', std) or ('one_plus_normal', std) for the random-weights mode.
     optional_alias: name of another tensor to use when this one is absent.
+    optional: the tensor may be absent; the part is then handed nothing for it and uses its own default.
     A dimension of -1 in `shape` is a size that only the stored tensor knows (the part reads it when it
     is handed the tensor); the random-weights mode cannot draw such a tensor.
     """
@@ -64,6 +65,7 @@ class ParamSpec:
     role: str = "matrix"
     init: Tuple[str, float] = ("normal", 0.02)
     optional_alias: Optional[str] = None
+    optional: bool = False            # may be absent from the stored weights: the part then falls back to its default
 
 
 class WeightSource:
@@ -215,6 +217,8 @@ def check_source(params: Dict[str, ParamSpec], source: WeightSource, where: str 
         if name not in have:
             if p.optional_alias is not None and p.optional_alias in params:
                 aliased[name] = p.optional_alias
+            elif p.optional:
+                pass
             else:
                 missing.append(name)
             continue

@@ -73,3 +73,14 @@ def test_options_that_may_be_absent():
     assert dict(plan.blocks[0].feed_forward.params)["groups"] is None
     rows_unknown = config_from_dict(_changed(gm.GUBI_A, ("layers", 0, "mixer", "bias_rows"), KeyError)).plan()
     assert rows_unknown.blocks[0].mixer.distance_bias == (-1, 40.0)           # only the stored table knows
+
+
+def test_one_stream_may_come_without_connection_tensors():
+    from litellmengine_b200.weights import DictSource
+    from litellmengine_b200.weights.loader import WeightError, check_source
+    w = gm.random_weights(gm.GUBI_D, 1)
+    params = model_parameters(config_from_dict(gm.GUBI_D).plan())
+    check_source(params, DictSource({n: t for n, t in w.items() if ".hc" not in n}))
+    two = gm.random_weights(gm.GUBI_A, 1)
+    with pytest.raises(WeightError):          # several streams need theirs
+        check_source(model_parameters(config_from_dict(gm.GUBI_A).plan()), DictSource({n: t for n, t in two.items() if ".hc" not in n}))

@@ -589,3 +589,15 @@ def test_tensor_core_prompt_attention_with_distance_bias_and_head_gate(d, window
         assert status.tolist() == [0, 0]
         got2 = out2[:, 16:].double().cpu().view(T, H, d)
         assert (got2[picked] - ref[picked]).abs().max() < 0.06, splits
+
+
+def test_one_stream_without_connection_tensors_is_the_plain_residual():
+    """`streams: 1` in a folder that stores no connection tensors: the model runs as one plainly added stream."""
+    cfg, page, w = model_of("D")
+    bare = {n: t for n, t in w.items() if ".hc" not in n}
+    plain_cfg = {k: v for k, v in cfg.items() if k != "streams"}
+    reqs = requests(cfg, [3, 41], seed=9)
+    ref = Reference(plain_cfg, bare, reqs, "float32")
+    steps = rh.trace_portions(reqs, seed=4)
+    runner = rh.make_runner(cfg, bare, "float32", page, rh.peak_tokens(steps, round_to=page), max_requests=2)
+    assert_close(rh.run_trace(runner, steps), ref, "float32", "one stream, no connection tensors")
