@@ -196,6 +196,16 @@ def test_trace_replay_and_prompt_command_on_a_model_folder(tmp_path):
     got1 = np.fromfile(out / "1.f32", dtype="<f4").reshape(1, -1)
     for row, pos in ((got0[0], 3), (got0[1], 24), (got1[0], 39)):
         assert _spread_error(row, ref[pos], spread) < 1e-4
+    # the prompt command: greedy tokens through the scheduler and the sampler
+    prompt = toks[:17]
+    ids = list(prompt)
+    for _ in range(6):
+        ids.append(int(pg.forward(cfg, w, ids)[-1].argmax()))
+    proc = subprocess.run([sys.executable, os.path.join(root, "bin", "run_prompt"), "--model", str(folder), "--input-ids",
+                           ",".join(map(str, prompt)), "--max-tokens", "6", "--dtype", "float32"],
+                          capture_output=True, text=True, timeout=600)
+    assert proc.returncode == 0, proc.stdout[-2000:] + proc.stderr[-2000:]
+    assert proc.stdout.strip().split("\n")[-1] == ",".join(map(str, ids[len(prompt):]))
 
 
 # ---- mechanisms alone -------------------------------------------------------------------------------

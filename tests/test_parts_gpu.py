@@ -53,7 +53,7 @@ def test_rmsnorm_part_and_rope_table():
     with pytest.raises(ValueError):
         lookup("position", "rope")(PositionSpec("rope", theta=1e4, rotary_dim=18), 16, DEV)
     with pytest.raises(KeyError, match="registered"):
-        lookup("norm", "layernorm")
+        lookup("norm", "batchnorm")
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
