@@ -57,7 +57,8 @@ __device__ __forceinline__ bf16* tile_at(bf16* base, int row, int chunk) {
     return base + row * D + ((chunk ^ (row & 7)) << 3);
 }
 
-template <int D, int AD_STAGES>
+// BIAS: a distance table joins the scores (an instantiation of its own, so that the plain kernel is what it was).
+template <int D, int AD_STAGES, bool BIAS>
 __global__ void __launch_bounds__(AD_THREADS) paged_decode_attention_kernel(
     const bf16* __restrict__ q, const bf16* __restrict__ cache, const int32_t* __restrict__ rows,
     const int32_t* __restrict__ positions, const int32_t* __restrict__ token_entry,
@@ -181,7 +182,7 @@ __global__ void __launch_bounds__(AD_THREADS) paged_decode_attention_kernel(
                 const int key = key0 + nb * 8 + (lane & 3) * 2 + c;
                 const bool vis = key < k_end;
                 float a0 = s[nb][c] * scale_log2e, a1 = s[nb][2 + c] * scale_log2e;
-                if (dist_bias && vis) {          // a learned bias by distance: a row of [heads, distances] per head, exp2 domain
+                if (BIAS && vis) {               // a learned bias by distance: a row of [heads, distances] per head, exp2 domain
                     const int dist = min(max(pos - key, 0), dist_len - 1);
                     a0 += __ldg(dist_bias + static_cast<size_t>(h0 + min(lane >> 2, G - 1)) * dist_len + dist);
                     a1 += __ldg(dist_bias + static_cast<size_t>(h0 + min((lane >> 2) + 8, G - 1)) * dist_len + dist);
@@ -309,7 +310,7 @@ static int launch_decode(const bf16* q, const bf16* cache, const int32_t* rows, 
                          int page_size, int window, float scale, int num_pages, int num_splits, int32_t* status,
                          const float* dist_bias, int dist_len, cudaStream_t s) {
     const size_t smem = static_cast<size_t>(16 + 2 * AD_STAGES * AD_BN) * D * sizeof(bf16);
-    auto kern = paged_decode_attention_kernel<D, AD_STAGES>;
+    auto kern = dist_bias ? paged_decode_attention_kernel<D, AD_STAGES, true> : paged_decode_attention_kernel<D, AD_STAGES, false>;
     if (smem > 48 * 1024) {
         const cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
         if (e != cudaSuccess) return static_cast<int>(e);
@@ -321,7 +322,7 @@ static int launch_decode(const bf16* q, const bf16* cache, const int32_t* rows, 
 #define TMA_GO(TS)                                                                                                   \
     {                                                                                                                \
         const size_t tsmem = static_cast<size_t>(2 * TS * AD_BN + 16) * D * sizeof(bf16) + 1024;                     \
-        auto tk = paged_decode_attention_tma_kernel<D, TS>;                                                          \
+        auto tk = dist_bias ? paged_decode_attention_tma_kernel<D, TS, true> : paged_decode_attention_tma_kernel<D, TS, false>; \
         const cudaError_t te = cudaFuncSetAttribute(tk, cudaFuncAttributeMaxDynamicSharedMemorySize,                 \
                                                     static_cast<int>(tsmem));                                        \
         if (te != cudaSuccess) return static_cast<int>(te);                                                          \

@@ -64,7 +64,7 @@ __device__ __forceinline__ bf16* tma_tile_at(bf16* base, int row, int chunk) {
     return base + (chunk >> 3) * (AD_BN * 64) + row * 64 + (((chunk & 7) ^ (row & 7)) << 3);
 }
 
-template <int D, int STAGES>
+template <int D, int STAGES, bool BIAS>
 __global__ void __launch_bounds__(AD_THREADS + 32) paged_decode_attention_tma_kernel(
     const __grid_constant__ CUtensorMap kv_map, const bf16* __restrict__ q, const int32_t* __restrict__ rows,
     const int32_t* __restrict__ positions, const int32_t* __restrict__ token_entry,
@@ -217,7 +217,7 @@ __global__ void __launch_bounds__(AD_THREADS + 32) paged_decode_attention_tma_ke
                     const int key = key0 + nb * 8 + (lane & 3) * 2 + c;
                     const bool vis = key < k_end && key >= k_begin;
                     float a0 = s[nb][c] * scale_log2e, a1 = s[nb][2 + c] * scale_log2e;
-                    if (dist_bias && vis) {      // a learned bias by distance: a row of [heads, distances] per head, exp2 domain
+                    if (BIAS && vis) {           // a learned bias by distance: a row of [heads, distances] per head, exp2 domain
                         const int dist = min(max(pos - key, 0), dist_len - 1);
                         a0 += __ldg(dist_bias + static_cast<size_t>(h0 + min(lane >> 2, G - 1)) * dist_len + dist);
                         a1 += __ldg(dist_bias + static_cast<size_t>(h0 + min((lane >> 2) + 8, G - 1)) * dist_len + dist);

@@ -55,7 +55,9 @@ __device__ __forceinline__ bf16* tile_at(bf16* base, int row, int chunk) {
     return base + row * D + ((chunk ^ (row & 7)) << 3);
 }
 
-template <int D>
+// EXT: the instantiation that takes a distance table, a gate per head, an output scale and an output column; the
+// plain one folds them away and is the kernel it was.
+template <int D, bool EXT>
 __global__ void __launch_bounds__(AP_THREADS) paged_prefill_attention_kernel(
     const bf16* __restrict__ q, bf16* __restrict__ out, const bf16* __restrict__ cache,
     const int32_t* __restrict__ tiles,            // [n_tiles][2]: entry index, first query row of the tile in the entry
@@ -146,7 +148,12 @@ __global__ void __launch_bounds__(AP_THREADS) paged_prefill_attention_kernel(
     const int lo1 = (window > 0 && pos1 - window + 1 > 0) ? pos1 - window + 1 : 0;
     const bool live0 = r0 < rows_here, live1 = r0 + 8 < rows_here;
     // a learned bias by distance, one row of [heads, distances] per head, already in the exp2 domain
-    const float* bias_h = dist_bias ? dist_bias + static_cast<size_t>(h) * dist_len : nullptr;
+    const float* bias_h = (EXT && dist_bias) ? dist_bias + static_cast<size_t>(h) * dist_len : nullptr;
+    if (!EXT) {
+        out_scale = 1.0f;
+        out_stride = static_cast<long long>(nq) * D;
+        out_off = 0;
+    }
 
     for (int it = 0; it < n_tiles; ++it) {
         const int kt = k_lo + it * AP_BN, buf = it & 1;
@@ -203,7 +210,7 @@ __global__ void __launch_bounds__(AP_THREADS) paged_prefill_attention_kernel(
             for (int c = 0; c < 2; ++c) {
                 const int key = kt + nb * 8 + (lane & 3) * 2 + c;
                 float a = s[nb][c] * scale_log2e, b2 = s[nb][2 + c] * scale_log2e;
-                if (bias_h) {
+                if (EXT && bias_h) {
                     a += __ldg(bias_h + min(max(pos0 - key, 0), dist_len - 1));
                     b2 += __ldg(bias_h + min(max(pos1 - key, 0), dist_len - 1));
                 }
@@ -261,7 +268,7 @@ __global__ void __launch_bounds__(AP_THREADS) paged_prefill_attention_kernel(
     cp_async_wait_all();
 
     float inv0 = live0 && l0 > 0.0f ? out_scale / l0 : 0.0f, inv1 = live1 && l1 > 0.0f ? out_scale / l1 : 0.0f;
-    if (head_gate) {                                  // one sigmoid gate per (token, head)
+    if (EXT && head_gate) {                           // one sigmoid gate per (token, head)
         if (live0) inv0 *= 1.0f / (1.0f + expf(-head_gate[static_cast<size_t>(row_base + r0) * gate_stride + gate_off + h]));
         if (live1) inv1 *= 1.0f / (1.0f + expf(-head_gate[static_cast<size_t>(row_base + r0 + 8) * gate_stride + gate_off + h]));
     }
@@ -316,9 +323,10 @@ extern "C" int llm_paged_attention_prefill_ex(
     cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
     dim3 grid(nq, n_tiles);
     const float scale_log2e = scale * 1.4426950408889634f;
+    const bool ext = dist_bias || head_gate || out_scale != 1.0f || out_off != 0 || out_stride != static_cast<long long>(nq) * d;
 #define LAUNCH(DD)                                                                                             \
     {                                                                                                          \
-        auto kern = paged_prefill_attention_kernel<DD>;                                                        \
+        auto kern = ext ? paged_prefill_attention_kernel<DD, true> : paged_prefill_attention_kernel<DD, false>;    \
         const cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,          \
                                                    static_cast<int>(smem));                                    \
         if (e != cudaSuccess) return static_cast<int>(e);                                                      \
